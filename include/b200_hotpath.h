@@ -671,6 +671,64 @@ int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int64_t ld_poo
                    int keep_first, void* out, int64_t ldo, int T, int H, int G, int D, int E,
                    const int* tok_list, int max_keys, int dtype, void* stream);
 
+/* b200_attn_extend_sink with one more option: v_head >= 0 makes every query head read the VALUES of
+ * key/value head v_head while its keys stay those of its own key/value head (v_head < 0: its own).
+ * Logit capping and a sink may be combined.                                                        */
+int b200_attn_extend_heads(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                           int64_t kv_row_stride, void* o, int64_t o_stride,
+                           const int32_t* req_to_token, int64_t req_to_token_stride,
+                           const int64_t* req_pool_indices, const int64_t* seq_lens,
+                           const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
+                           const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq, int Hkv,
+                           int D, int Dv, float scale, float logit_cap, float out_scale, int causal,
+                           int window, int keep_first, const float* sink, int v_head, int dtype,
+                           void* stream);
+/* b200_qk_norm_rope_write with the further options: queries times 1 + temp_coef * ln(floor((p + 1) /
+ * temp_every) + 1) (temp_every 0: none); v_norm != 0: every value head divided by its root mean square
+ * (eps, no weight); first_pool given: v <- (1 - *v_mix) v + *v_mix * first_pool[loc[t]][first_off ...]
+ * (another layer's row of the same token, same G and E).                                            */
+int b200_qkv_prep_write(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                        int64_t ldv, const float* qw, const float* kw, int q_group, int k_group,
+                        float eps, const float* freq_hi, const float* freq_lo, int rot_dims,
+                        const int* tok_pos, const int64_t* loc, void* pool, int64_t ld_pool, int k_off,
+                        int v_off, float* q_out, int64_t ldqo, void* q_out16, int64_t ldqo16, int T,
+                        int H, int G, int D, int E, float temp_coef, int temp_every, int v_norm,
+                        const float* v_mix, const void* first_pool, int64_t ld_first, int first_off,
+                        int dtype, void* stream);
+/* b200_sink_attn with a soft cap on the scaled scores (softcap > 0: cap * tanh(s / cap)) and, with
+ * all_values != 0, the weights of every query head applied to the values of EVERY key/value head:
+ * out is then fp32, G planes of ldo_plane elements, each [T rows of ldo][H, E].                     */
+int b200_sink_attn_heads(const float* q, int64_t ldq, const void* pool, int64_t ld_pool, int k_off,
+                         int v_off, const int* req_to_token, int64_t ld_r2t, const int64_t* req_idx,
+                         const int* tok_pos, const int* tok_b, const float* sink, float scale,
+                         float softcap, int window, int keep_first, void* out, int64_t ldo,
+                         int all_values, int64_t ldo_plane, int T, int H, int G, int D, int E,
+                         const int* tok_list, int max_keys, int dtype, void* stream);
+/* out[t, h, :] = sigmoid(gate[t, h]) * sum_g mix[h, g] * a[plane h / (H / G)][t][g, :]  (gate NULL: 1):
+ * heads' softmax weights mixed after the softmax, as a combination of per-head products.  a in
+ * a_dtype (the activations' dtype or fp32), the sum in fp32.                                        */
+int b200_head_mix_gate(const void* a, int64_t lda, int64_t lda_plane, int a_dtype, const float* mix,
+                       const void* gate, int64_t ldg, void* out, int64_t ldo, int T, int H, int G,
+                       int E, int dtype, void* stream);
+/* out[t, h * E + e] = x[t * ldx_t + h * ldx_h + e] * sigmoid(g[t, per_head ? h : h * E + e]).        */
+int b200_sigmoid_gate_mul(const void* x, int64_t ldx_t, int64_t ldx_h, const void* g, int64_t ldg,
+                          int per_head, void* out, int64_t ldo, int T, int H, int E, int dtype,
+                          void* stream);
+/* b200_add_normed whose optional copy is the next sublayer's pre-norm of the new residual:
+ * out_h = x / sqrt(mean(x^2) + eps) * w_next (w_next NULL: the plain copy).                         */
+int b200_add_normed_next(float* x, int64_t ldx, const void* a, int64_t lda, float sa, const void* b,
+                         int64_t ldb, float sb, const void* rows, int64_t ld_rows, int top,
+                         const float* w, float eps, float mult, void* out_h, int64_t ldh,
+                         const float* w_next, int T, int W, int dtype, void* stream);
+/* b200_latent_prep whose rotated key coordinates are multiplied by rot_scale after the rotation (a
+ * scaled rotation multiplies sine and cosine by a factor on both the query and the key side; the
+ * product of the two factors is applied here once).                                                */
+int b200_latent_prep_scaled(const void* qraw, int64_t ldq, int QR, const float* wq, void* cq,
+                            int64_t ldcq, const void* kvraw, int64_t ldkv, int R, int rot, int rot_dims,
+                            const float* wkv, const float* inv_freq, const int* tok_pos,
+                            const int64_t* loc, void* cache, int64_t ldc, float eps, float rot_scale,
+                            int T, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

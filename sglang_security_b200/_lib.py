@@ -212,6 +212,32 @@ _SIGNATURES = {
     "b200_sink_attn": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p,
                                c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "b200_attn_extend_heads": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p,
+                                       c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_float, c_float, c_float, c_int, c_int, c_int, c_void_p, c_int,
+                                       c_int, c_void_p]),
+    "b200_qkv_prep_write": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                    c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
+                                    c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
+                                    c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                                    c_float, c_int, c_int, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                    c_void_p]),
+    "b200_sink_attn_heads": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int,
+                                     c_int, c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_int, c_int,
+                                     c_int, c_void_p, c_int, c_int, c_void_p]),
+    "b200_head_mix_gate": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64,
+                                   c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_sigmoid_gate_mul": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_void_p,
+                                      c_int64, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_add_normed_next": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_float, c_void_p, c_int64,
+                                     c_float, c_void_p, c_int64, c_int, c_void_p, c_float, c_float,
+                                     c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_latent_prep_scaled": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p,
+                                        c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_int64, c_float, c_float, c_int, c_int,
+                                        c_void_p]),
 }
 
 

@@ -50,6 +50,8 @@ struct ExtendParams {
   int window;                    // causal sliding window: row at position i sees i - window < j <= i (0 = all)
   int keep_first;                // with a window: keys j < keep_first stay visible outside it
   const float* sink;             // [Hq] or NULL: exp(sink[h]) joins the softmax denominator, no key or value
+  int v_head;                    // >= 0: every query head reads the values of this key/value head (keys
+                                 // stay those of its own); < 0: its own key/value head's
 };
 
 constexpr int kExtThreads = 256;
@@ -165,7 +167,8 @@ attn_extend_kernel(const ExtendParams p) {
     const int32_t* rtt = p.req_to_token + p.req_pool_indices[b] * p.rtt_stride;
     const int64_t row_bytes = p.kv_row_stride * 2;
     const char* kbase = static_cast<const char*>(p.k_cache) + static_cast<int64_t>(kvh) * D * 2;
-    const char* vbase = static_cast<const char*>(p.v_cache) + static_cast<int64_t>(kvh) * D * 2;
+    const char* vbase = static_cast<const char*>(p.v_cache) +
+                        static_cast<int64_t>(p.v_head >= 0 ? p.v_head : kvh) * D * 2;
     // Q tile: row r = (token r / pack, head r % pack)
     for (int c = lt; c < 128 * CPR; c += kLoaders) {
       const int r = c / CPR, col = c - r * CPR;
@@ -284,7 +287,12 @@ attn_extend_kernel(const ExtendParams p) {
 
     auto score = [&](uint32_t raw, int kpos) -> float {
       float s = __uint_as_float(raw) * p.qk_scale;
-      if (capped) s = cap_log2 * fast_tanh(s * inv_cap);
+      if (capped) {
+        // tanh(x) = 1 - 2 / (e^(2x) + 1): absolute error of a few 1e-7, where the one-instruction
+        // approximation is off by 5e-4 of the cap (a visible share of a weight at a cap of tens)
+        const float e2 = fast_exp2(s * inv_cap * 2.8853900817779268f);
+        s = cap_log2 * (1.0f - __fdividef(2.0f, e2 + 1.0f));
+      }
       return (kpos <= limit && (kpos >= first || kpos < kept)) ? s : -INFINITY;
     };
 
@@ -535,9 +543,25 @@ int b200_attn_extend_sink(const void* q, int64_t q_stride, const void* k_cache, 
                           const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq, int Hkv,
                           int D, int Dv, float scale, float logit_cap, float out_scale, int causal,
                           int window, int keep_first, const float* sink, int dtype, void* stream) {
+  return b200_attn_extend_heads(q, q_stride, k_cache, v_cache, kv_row_stride, o, o_stride, req_to_token,
+                                req_to_token_stride, req_pool_indices, seq_lens, extend_prefix_lens,
+                                extend_seq_lens, extend_start_loc, bs, max_extend_len, Hq, Hkv, D, Dv,
+                                scale, logit_cap, out_scale, causal, window, keep_first, sink, -1, dtype,
+                                stream);
+}
+
+int b200_attn_extend_heads(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                           int64_t kv_row_stride, void* o, int64_t o_stride,
+                           const int32_t* req_to_token, int64_t req_to_token_stride,
+                           const int64_t* req_pool_indices, const int64_t* seq_lens,
+                           const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
+                           const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq, int Hkv,
+                           int D, int Dv, float scale, float logit_cap, float out_scale, int causal,
+                           int window, int keep_first, const float* sink, int v_head, int dtype,
+                           void* stream) {
   using namespace b200;
-  B200_REQUIRE(keep_first >= 0 && (!sink || logit_cap <= 0.f),
-               "b200_attn_extend: kept tokens %d; a sink excludes logit capping", keep_first);
+  B200_REQUIRE(keep_first >= 0 && v_head < Hkv, "b200_attn_extend: kept tokens %d, value head %d",
+               keep_first, v_head);
   B200_REQUIRE(window >= 0 && (window == 0 || causal), "b200_attn_extend: a window needs causal");
   if (bs == 0 || max_extend_len == 0) return 0;
   B200_REQUIRE(q && k_cache && v_cache && o && req_to_token && req_pool_indices && seq_lens &&
@@ -582,6 +606,7 @@ int b200_attn_extend_sink(const void* q, int64_t q_stride, const void* k_cache, 
   p.window = window;
   p.keep_first = window > 0 ? keep_first : 0;
   p.sink = sink;
+  p.v_head = v_head;
   B200_REQUIRE(bs <= 65535 && Hkv * p.head_tiles <= 65535, "b200_attn_extend: grid too large");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == B200_BF16)

@@ -48,7 +48,8 @@ latent_prep_kernel(const T* __restrict__ qraw, int64_t ldq, int QR, const float*
                    T* __restrict__ cq, int64_t ldcq, const T* __restrict__ kvraw, int64_t ldkv, int R,
                    int rot, int rot_dims, const float* __restrict__ wkv,
                    const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
-                   const int64_t* __restrict__ loc, T* __restrict__ cache, int64_t ldc, float eps) {
+                   const int64_t* __restrict__ loc, T* __restrict__ cache, int64_t ldc, float eps,
+                   float rot_scale) {
   __shared__ float red[kPrepThreads / 32];
   const int t = blockIdx.x;
   if (qraw) {
@@ -78,7 +79,11 @@ latent_prep_kernel(const T* __restrict__ qraw, int64_t ldq, int QR, const float*
       float u = to_float<T>(row[R + 2 * i]);
       if (2 * i + 1 < rot) {
         float v = to_float<T>(row[R + 2 * i + 1]);
-        if (2 * i + 1 < rot_dims) rotate_pair(u, v, pos, inv_freq[i]);
+        if (2 * i + 1 < rot_dims) {
+          rotate_pair(u, v, pos, inv_freq[i]);
+          u *= rot_scale;
+          v *= rot_scale;
+        }
         dst[R + 2 * i + 1] = from_float<T>(v);
       }
       dst[R + 2 * i] = from_float<T>(u);
@@ -384,11 +389,12 @@ static bool latent_attn_mma_enabled() {
 
 }  // namespace b200
 
-extern "C" int b200_latent_prep(const void* qraw, int64_t ldq, int QR, const float* wq, void* cq,
+extern "C" int b200_latent_prep_scaled(const void* qraw, int64_t ldq, int QR, const float* wq, void* cq,
                                 int64_t ldcq, const void* kvraw, int64_t ldkv, int R, int rot,
                                 int rot_dims, const float* wkv, const float* inv_freq,
                                 const int* tok_pos, const int64_t* loc, void* cache, int64_t ldc,
-                                float eps, int T, int dtype, void* stream) {
+                                float eps, float rot_scale, int T, int dtype,
+                                       void* stream) {
   using namespace b200;
   if (T == 0) return 0;
   B200_REQUIRE(qraw || kvraw, "b200_latent_prep: nothing to do");
@@ -402,7 +408,7 @@ extern "C" int b200_latent_prep(const void* qraw, int64_t ldq, int QR, const flo
   launch_kernel(latent_prep_kernel<TT>, dim3(T), dim3(kPrepThreads), 0, st, 1, 0,                    \
                 static_cast<const TT*>(qraw), ldq, QR, wq, static_cast<TT*>(cq), ldcq,               \
                 static_cast<const TT*>(kvraw), ldkv, R, rot, rot_dims, wkv, inv_freq, tok_pos, loc,  \
-                static_cast<TT*>(cache), ldc, eps)
+                static_cast<TT*>(cache), ldc, eps, rot_scale)
   if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
   else if (dtype == B200_F16) LAUNCH(__half);
   else if (dtype == B200_F32) LAUNCH(float);
@@ -410,6 +416,15 @@ extern "C" int b200_latent_prep(const void* qraw, int64_t ldq, int QR, const flo
 #undef LAUNCH
   B200_CHECK_LAUNCH("latent_prep_kernel");
   return 0;
+}
+
+extern "C" int b200_latent_prep(const void* qraw, int64_t ldq, int QR, const float* wq, void* cq,
+                                int64_t ldcq, const void* kvraw, int64_t ldkv, int R, int rot,
+                                int rot_dims, const float* wkv, const float* inv_freq,
+                                const int* tok_pos, const int64_t* loc, void* cache, int64_t ldc,
+                                float eps, int T, int dtype, void* stream) {
+  return b200_latent_prep_scaled(qraw, ldq, QR, wq, cq, ldcq, kvraw, ldkv, R, rot, rot_dims, wkv,
+                                 inv_freq, tok_pos, loc, cache, ldc, eps, 1.0f, T, dtype, stream);
 }
 
 extern "C" int b200_latent_attn(const float* q_lat, int64_t ldql_t, int64_t ldql_h, const void* q_raw,

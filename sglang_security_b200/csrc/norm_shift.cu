@@ -10,7 +10,9 @@
 //   add_normed           : for designs whose norm sits on a sublayer's OUTPUT: y = sa * a + sb * b +
 //                          sum_k rows[t * top + k] (all terms optional) in fp32, then
 //                          x += mult * y / sqrt(mean(y^2) + eps) * w[d]; optionally also writes the new x
-//                          in the model dtype, the next sublayer's input
+//                          in the model dtype, the next sublayer's input; with a second weight the copy is
+//                          the NEXT sublayer's pre-norm instead, x / sqrt(mean(x^2) + eps) * w_next (designs
+//                          with a norm on both sides of every sublayer: one launch per sublayer boundary)
 //   softcap_rows         : out = cap * tanh(z / cap) in fp32
 #include "common.cuh"
 
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(kRowThreads)
 add_normed_kernel(float* __restrict__ x, int64_t ldx, const TA* __restrict__ a, int64_t lda, float sa,
                   const TA* __restrict__ b, int64_t ldb, float sb, const TA* __restrict__ y,
                   int64_t ldy, int top, const float* __restrict__ w, float eps, float mult,
-                  TA* __restrict__ out_h, int64_t ldh, int W) {
+                  TA* __restrict__ out_h, int64_t ldh, int W, const float* __restrict__ w_next) {
   __shared__ float red[kRowThreads / 32];
   const int t = blockIdx.x;
   auto term = [&](int d) {
@@ -154,11 +156,19 @@ add_normed_kernel(float* __restrict__ x, int64_t ldx, const TA* __restrict__ a, 
   }
   s = block_sum(s, red);
   const float r = mult / sqrtf(s / static_cast<float>(W) + eps);
+  float s2 = 0.f;
   for (int d = threadIdx.x; d < W; d += kRowThreads) {
     const float nx = fmaf(term(d) * r, w ? w[d] : 1.f, x[t * ldx + d]);
     x[t * ldx + d] = nx;
-    if (out_h) out_h[t * ldh + d] = from_float<TA>(nx);
+    s2 = fmaf(nx, nx, s2);
+    if (out_h && !w_next) out_h[t * ldh + d] = from_float<TA>(nx);
   }
+  if (!out_h || !w_next) return;
+  // the next sublayer's pre-norm of the new residual (each thread re-reads the elements it wrote)
+  s2 = block_sum(s2, red);
+  const float r2 = 1.0f / sqrtf(s2 / static_cast<float>(W) + eps);
+  for (int d = threadIdx.x; d < W; d += kRowThreads)
+    out_h[t * ldh + d] = from_float<TA>(x[t * ldx + d] * r2 * w_next[d]);
 }
 
 template <typename T>
@@ -244,21 +254,23 @@ extern "C" int b200_act_and_mul(const void* z, int64_t ldz, void* out, int64_t l
   return 0;
 }
 
-extern "C" int b200_add_normed(float* x, int64_t ldx, const void* a, int64_t lda, float sa,
-                               const void* b, int64_t ldb, float sb, const void* rows, int64_t ld_rows,
-                               int top, const float* w, float eps, float mult, void* out_h, int64_t ldh,
-                               int T, int W, int dtype, void* stream) {
+extern "C" int b200_add_normed_next(float* x, int64_t ldx, const void* a, int64_t lda, float sa,
+                                    const void* b, int64_t ldb, float sb, const void* rows,
+                                    int64_t ld_rows, int top, const float* w, float eps, float mult,
+                                    void* out_h, int64_t ldh, const float* w_next, int T, int W,
+                                    int dtype, void* stream) {
   using namespace b200;
   if (T == 0) return 0;
   B200_REQUIRE(x && (a || b || rows) && T > 0 && W > 0, "b200_add_normed: bad arguments");
   B200_REQUIRE(!rows || top > 0, "b200_add_normed: rows without a count per token");
+  B200_REQUIRE(!w_next || out_h, "b200_add_normed: a next norm without an output");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ScopedKernelTimer timer("add_normed", st);
 #define LAUNCH(TA)                                                                                   \
   launch_kernel(add_normed_kernel<TA>, dim3(T), dim3(kRowThreads), 0, st, 1, 0, x, ldx,             \
                 static_cast<const TA*>(a), lda, sa, static_cast<const TA*>(b), ldb, sb,              \
                 static_cast<const TA*>(rows), ld_rows, top, w, eps, mult, static_cast<TA*>(out_h),   \
-                ldh, W)
+                ldh, W, w_next)
   if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
   else if (dtype == B200_F16) LAUNCH(__half);
   else if (dtype == B200_F32) LAUNCH(float);
@@ -266,6 +278,14 @@ extern "C" int b200_add_normed(float* x, int64_t ldx, const void* a, int64_t lda
 #undef LAUNCH
   B200_CHECK_LAUNCH("add_normed_kernel");
   return 0;
+}
+
+extern "C" int b200_add_normed(float* x, int64_t ldx, const void* a, int64_t lda, float sa,
+                               const void* b, int64_t ldb, float sb, const void* rows, int64_t ld_rows,
+                               int top, const float* w, float eps, float mult, void* out_h, int64_t ldh,
+                               int T, int W, int dtype, void* stream) {
+  return b200_add_normed_next(x, ldx, a, lda, sa, b, ldb, sb, rows, ld_rows, top, w, eps, mult, out_h,
+                              ldh, nullptr, T, W, dtype, stream);
 }
 
 extern "C" int b200_softcap_rows(const void* z, int64_t ldz, float* out, int64_t ldo, int T, int V,

@@ -6,7 +6,14 @@
 //   * a causal sliding window that also keeps the first `keep_first` tokens of the sequence visible
 //     (at their true positions);
 //   * a learned sink per query head: exp(sink) joins the softmax denominator, with no key or value;
-//   * key size D and value size E that differ.
+//   * key size D and value size E that differ;
+//   * a query temperature that grows with the position in steps: q *= 1 + coef * ln(floor((p + 1) / every) + 1);
+//   * RMS norm of each value head (no weight), and a mix of the normed values with the values another
+//     layer cached for the same token: v <- (1 - lambda) v + lambda v_first;
+//   * a soft cap on the scaled scores: s <- cap * tanh(s / cap);
+//   * the weights of every query head applied to the values of EVERY key/value head (one grid plane
+//     per value head), for designs that mix the heads' weights after the softmax: the mixed output is
+//     a linear combination of these per-head products (csrc/head_mix.cu).
 //
 //   qk_norm_rope_write : per token, from the projection outputs: q -> norm -> rotation -> fp32 queries;
 //                        k -> norm -> rotation -> pool row; v -> pool row.  Norms and angles in fp32;
@@ -76,7 +83,9 @@ qk_norm_rope_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
                           int rot_dims, const int* __restrict__ tok_pos,
                           const int64_t* __restrict__ loc, TP* __restrict__ pool, int64_t ld_pool,
                           int k_off, int v_off, float* __restrict__ q_out, int64_t ldqo,
-                          T* __restrict__ q_out16, int64_t ldqo16, int H, int G, int D, int E) {
+                          T* __restrict__ q_out16, int64_t ldqo16, int H, int G, int D, int E,
+                          float temp_coef, int temp_every, int v_norm, const float* __restrict__ v_mix,
+                          const TP* __restrict__ first_pool, int64_t ld_first, int first_off) {
   extern __shared__ float prep_smem[];       // [rot_dims / 2] cos, [rot_dims / 2] sin, group scales
   __shared__ float red[kPrepThreads / 32];
   const int t = blockIdx.x, half = rot_dims / 2;
@@ -96,6 +105,10 @@ qk_norm_rope_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
   }
   const T* qr = q + t * ldq;
   const T* kr = k + t * ldk;
+  // query temperature: a step function of the position, fp32
+  const float temp = temp_every > 0
+                         ? 1.0f + temp_coef * logf(static_cast<float>((tok_pos[t] + 1) / temp_every) + 1.0f)
+                         : 1.0f;
   if (q_group > 0) group_inv_rms(qr, H * D, q_group, eps, inv_q, red);
   if (k_group > 0) group_inv_rms(kr, G * D, k_group, eps, inv_k, red);
   __syncthreads();
@@ -115,6 +128,7 @@ qk_norm_rope_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
       x = (d & 1) ? fmaf(x, c, y * s) : fmaf(x, c, -y * s);
     }
     if (is_q) {
+      x *= temp;
       if (q_out) q_out[t * ldqo + i] = x;
       if (q_out16) q_out16[t * ldqo16 + i] = from_float<T>(x);
     } else {
@@ -122,8 +136,33 @@ qk_norm_rope_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
     }
   }
   const T* vr = v + t * ldv;
-  for (int i = threadIdx.x; i < G * E; i += kPrepThreads)
-    prow[v_off + i] = from_float<TP>(to_float<T>(vr[i]));
+  if (!v_norm && !first_pool) {
+    for (int i = threadIdx.x; i < G * E; i += kPrepThreads)
+      prow[v_off + i] = from_float<TP>(to_float<T>(vr[i]));
+    return;
+  }
+  // one warp per value head: unit RMS over the head (fp32), then the mix with the first layer's row
+  const TP* first = first_pool ? first_pool + loc[t] * ld_first + first_off : nullptr;
+  const float lam = (first && v_mix) ? *v_mix : 0.f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int g = warp; g < G; g += kPrepThreads / 32) {
+    float inv = 1.f;
+    if (v_norm) {
+      float ss = 0.f;
+      for (int e = lane; e < E; e += 32) {
+        const float x = to_float<T>(vr[g * E + e]);
+        ss = fmaf(x, x, ss);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      inv = 1.0f / sqrtf(ss / static_cast<float>(E) + eps);
+    }
+    for (int e = lane; e < E; e += 32) {
+      float x = to_float<T>(vr[g * E + e]) * inv;
+      if (first) x = (1.0f - lam) * x + lam * to_float<TP>(first[g * E + e]);
+      prow[v_off + g * E + e] = from_float<TP>(x);
+    }
+  }
 }
 
 constexpr int kSinkMaxWarps = 16;  // warps per CTA: 4 to 16, by the longest key list (host)
@@ -137,7 +176,7 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
                  int64_t ld_r2t, const int64_t* __restrict__ req_idx, const int* __restrict__ tok_pos,
                  const int* __restrict__ tok_b, const float* __restrict__ sink, float scale, int window,
                  int keep_first, TO* __restrict__ out, int64_t ldo, int H, int G, int D, int E,
-                 const int* __restrict__ tok_list) {
+                 const int* __restrict__ tok_list, float softcap, int64_t ldo_plane) {
   extern __shared__ __align__(16) float sink_smem[];
   constexpr int RH = kSinkHeads;
   const int nw = blockDim.x >> 5;
@@ -148,6 +187,10 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
   float* wf = wl + nw * RH;                    // [nw][RH] merge factors
   float* wt = wf + nw * RH;                    // [RH] merged denominators
   const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x, g = blockIdx.y, R = H / G;
+  // value head: the key/value head's own, or (one grid plane per value head) plane z
+  const int gv = gridDim.z > 1 ? static_cast<int>(blockIdx.z) : g;
+  out += static_cast<int64_t>(blockIdx.z) * ldo_plane;
+  const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int p = tok_pos[t];
   const int* r2t = req_to_token + req_idx[tok_b[t]] * ld_r2t;
@@ -158,7 +201,7 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
   const bool vec = (D % 8 == 0) && sizeof(TP) == 2 && (ld_pool % 8 == 0) && ((k_off + g * D) % 8 == 0) &&
                    ((reinterpret_cast<uintptr_t>(pool) & 15) == 0);
   // values: 4 consecutive columns per lane with vector loads when every piece is aligned
-  const bool vblk = (E % 4 == 0) && (ld_pool % 4 == 0) && ((v_off + g * E) % 4 == 0) &&
+  const bool vblk = (E % 4 == 0) && (ld_pool % 4 == 0) && ((v_off + gv * E) % 4 == 0) &&
                     ((reinterpret_cast<uintptr_t>(pool) & 15) == 0);
   // the query heads that share this key/value head, RH at a time: their keys and values are read once
   // per pass
@@ -221,6 +264,10 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
           }
         }
       }
+      if (softcap > 0.f) {
+#pragma unroll
+        for (int r = 0; r < RH; ++r) s[r] = softcap * tanhf(s[r] * inv_cap);
+      }
       float pj[RH];
 #pragma unroll
       for (int r = 0; r < RH; ++r) {
@@ -255,7 +302,7 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int64_t sl = __shfl_sync(0xffffffffu, slot, (j0 + i) & 31);   // lanes past cnt hold slot 0
-              u[i] = *reinterpret_cast<const V4*>(pool + sl * ld_pool + v_off + g * E + (col_ok ? e : 0));
+              u[i] = *reinterpret_cast<const V4*>(pool + sl * ld_pool + v_off + gv * E + (col_ok ? e : 0));
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -287,7 +334,7 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
           float pw[RH];
 #pragma unroll
           for (int r = 0; r < RH; ++r) pw[r] = __shfl_sync(0xffffffffu, pj[r], jj);
-          const TP* vr = pool + sl * ld_pool + v_off + g * E;
+          const TP* vr = pool + sl * ld_pool + v_off + gv * E;
 #pragma unroll
           for (int c = 0; c < kSinkMaxCols; ++c) {
             const int e = lane + 32 * c;
@@ -338,6 +385,50 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
 
 }  // namespace b200
 
+extern "C" int b200_qkv_prep_write(const void* q, int64_t ldq, const void* k, int64_t ldk,
+                                   const void* v, int64_t ldv, const float* qw, const float* kw,
+                                   int q_group, int k_group, float eps, const float* freq_hi,
+                                   const float* freq_lo, int rot_dims, const int* tok_pos,
+                                   const int64_t* loc, void* pool, int64_t ld_pool, int k_off,
+                                   int v_off, float* q_out, int64_t ldqo, void* q_out16,
+                                   int64_t ldqo16, int T, int H, int G, int D, int E, float temp_coef,
+                                   int temp_every, int v_norm, const float* v_mix,
+                                   const void* first_pool, int64_t ld_first, int first_off, int dtype,
+                                   void* stream) {
+  using namespace b200;
+  if (T == 0) return 0;
+  B200_REQUIRE(q && k && v && tok_pos && loc && pool && (q_out || q_out16),
+               "b200_qkv_prep_write: null pointer");
+  B200_REQUIRE(T > 0 && H > 0 && G > 0 && D > 0 && E > 0 && rot_dims >= 0 && rot_dims <= D &&
+                   rot_dims % 2 == 0 && (rot_dims == 0 || freq_hi),
+               "b200_qkv_prep_write: head size %d, rotated %d", D, rot_dims);
+  B200_REQUIRE((q_group == 0 || (H * D) % q_group == 0) && (k_group == 0 || (G * D) % k_group == 0) &&
+                   q_group >= 0 && k_group >= 0,
+               "b200_qkv_prep_write: norm groups %d / %d do not divide the projections", q_group,
+               k_group);
+  B200_REQUIRE(temp_every >= 0 && (!first_pool || v_mix),
+               "b200_qkv_prep_write: temperature step %d; a value mix needs its weight", temp_every);
+  const size_t smem = sizeof(float) * (rot_dims + (q_group ? H * D / q_group : 0) +
+                                       (k_group ? G * D / k_group : 0) + 1);
+  B200_REQUIRE(smem <= 48 * 1024, "b200_qkv_prep_write: too many norm groups");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("qk_norm_rope_write", st);
+#define LAUNCH(TT)                                                                                   \
+  launch_kernel(qk_norm_rope_write_kernel<TT, TT>, dim3(T), dim3(kPrepThreads), smem, st, 1, 0,      \
+                static_cast<const TT*>(q), ldq, static_cast<const TT*>(k), ldk,                      \
+                static_cast<const TT*>(v), ldv, qw, kw, q_group, k_group, eps, freq_hi, freq_lo,     \
+                rot_dims, tok_pos, loc, static_cast<TT*>(pool), ld_pool, k_off, v_off, q_out, ldqo,  \
+                static_cast<TT*>(q_out16), ldqo16, H, G, D, E, temp_coef, temp_every, v_norm, v_mix, \
+                static_cast<const TT*>(first_pool), ld_first, first_off)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else if (dtype == B200_F32) LAUNCH(float);
+  else B200_REQUIRE(false, "b200_qkv_prep_write: dtype %d", dtype);
+#undef LAUNCH
+  B200_CHECK_LAUNCH("qk_norm_rope_write_kernel");
+  return 0;
+}
+
 extern "C" int b200_qk_norm_rope_write(const void* q, int64_t ldq, const void* k, int64_t ldk,
                                        const void* v, int64_t ldv, const float* qw, const float* kw,
                                        int q_group, int k_group, float eps, const float* freq_hi,
@@ -346,49 +437,27 @@ extern "C" int b200_qk_norm_rope_write(const void* q, int64_t ldq, const void* k
                                        int v_off, float* q_out, int64_t ldqo, void* q_out16,
                                        int64_t ldqo16, int T, int H, int G, int D, int E, int dtype,
                                        void* stream) {
-  using namespace b200;
-  if (T == 0) return 0;
-  B200_REQUIRE(q && k && v && tok_pos && loc && pool && (q_out || q_out16),
-               "b200_qk_norm_rope_write: null pointer");
-  B200_REQUIRE(T > 0 && H > 0 && G > 0 && D > 0 && E > 0 && rot_dims >= 0 && rot_dims <= D &&
-                   rot_dims % 2 == 0 && (rot_dims == 0 || freq_hi),
-               "b200_qk_norm_rope_write: head size %d, rotated %d", D, rot_dims);
-  B200_REQUIRE((q_group == 0 || (H * D) % q_group == 0) && (k_group == 0 || (G * D) % k_group == 0) &&
-                   q_group >= 0 && k_group >= 0,
-               "b200_qk_norm_rope_write: norm groups %d / %d do not divide the projections", q_group,
-               k_group);
-  const size_t smem = sizeof(float) * (rot_dims + (q_group ? H * D / q_group : 0) +
-                                       (k_group ? G * D / k_group : 0) + 1);
-  B200_REQUIRE(smem <= 48 * 1024, "b200_qk_norm_rope_write: too many norm groups");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  ScopedKernelTimer timer("qk_norm_rope_write", st);
-#define LAUNCH(TT)                                                                                   \
-  launch_kernel(qk_norm_rope_write_kernel<TT, TT>, dim3(T), dim3(kPrepThreads), smem, st, 1, 0,      \
-                static_cast<const TT*>(q), ldq, static_cast<const TT*>(k), ldk,                      \
-                static_cast<const TT*>(v), ldv, qw, kw, q_group, k_group, eps, freq_hi, freq_lo,     \
-                rot_dims, tok_pos, loc, static_cast<TT*>(pool), ld_pool, k_off, v_off, q_out, ldqo,  \
-                static_cast<TT*>(q_out16), ldqo16, H, G, D, E)
-  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
-  else if (dtype == B200_F16) LAUNCH(__half);
-  else if (dtype == B200_F32) LAUNCH(float);
-  else B200_REQUIRE(false, "b200_qk_norm_rope_write: dtype %d", dtype);
-#undef LAUNCH
-  B200_CHECK_LAUNCH("qk_norm_rope_write_kernel");
-  return 0;
+  return b200_qkv_prep_write(q, ldq, k, ldk, v, ldv, qw, kw, q_group, k_group, eps, freq_hi, freq_lo,
+                             rot_dims, tok_pos, loc, pool, ld_pool, k_off, v_off, q_out, ldqo, q_out16,
+                             ldqo16, T, H, G, D, E, 0.f, 0, 0, nullptr, nullptr, 0, 0, dtype, stream);
 }
 
-extern "C" int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int64_t ld_pool, int k_off,
-                              int v_off, const int* req_to_token, int64_t ld_r2t,
-                              const int64_t* req_idx, const int* tok_pos, const int* tok_b,
-                              const float* sink, float scale, int window, int keep_first, void* out,
-                              int64_t ldo, int T, int H, int G, int D, int E, const int* tok_list,
-                              int max_keys, int dtype, void* stream) {
+// softcap > 0: scores are capped (cap * tanh(s / cap)) before the softmax.  all_values != 0: the weights
+// of every query head are applied to the values of every key/value head; `out` is then fp32
+// [G planes][T rows of ldo][H, E] with `ldo_plane` elements between planes.
+extern "C" int b200_sink_attn_heads(const float* q, int64_t ldq, const void* pool, int64_t ld_pool,
+                                    int k_off, int v_off, const int* req_to_token, int64_t ld_r2t,
+                                    const int64_t* req_idx, const int* tok_pos, const int* tok_b,
+                                    const float* sink, float scale, float softcap, int window,
+                                    int keep_first, void* out, int64_t ldo, int all_values,
+                                    int64_t ldo_plane, int T, int H, int G, int D, int E,
+                                    const int* tok_list, int max_keys, int dtype, void* stream) {
   using namespace b200;
   if (T == 0) return 0;
   B200_REQUIRE(q && pool && req_to_token && req_idx && tok_pos && tok_b && out,
                "b200_sink_attn: null pointer");
   B200_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && E > 0 && E <= 32 * kSinkMaxCols &&
-                   window >= 0 && keep_first >= 0 && G <= 65535,
+                   window >= 0 && keep_first >= 0 && G <= 65535 && softcap >= 0.f,
                "b200_sink_attn: heads %d / %d, key size %d, value size %d (max %d)", H, G, D, E,
                32 * kSinkMaxCols);
   // one warp per 64 keys of the longest list (a hint; 0 = unknown): a warp's tiles are dependent round
@@ -403,17 +472,36 @@ extern "C" int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int
   B200_REQUIRE(smem <= 48 * 1024, "b200_sink_attn: key size %d too large", D);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ScopedKernelTimer timer("sink_attn", st);
-  const dim3 grid(T, G);
-#define LAUNCH(TT)                                                                                   \
-  launch_kernel(sink_attn_kernel<TT, TT>, grid, dim3(nw * 32), smem, st, 1, 0, q, ldq,               \
+  const dim3 grid(T, G, all_values && G > 1 ? G : 1);
+  if (!(all_values && G > 1)) ldo_plane = 0;
+#define LAUNCH(TT, TO)                                                                               \
+  launch_kernel(sink_attn_kernel<TT, TO>, grid, dim3(nw * 32), smem, st, 1, 0, q, ldq,               \
                 static_cast<const TT*>(pool), ld_pool, k_off, v_off, req_to_token, ld_r2t, req_idx,  \
-                tok_pos, tok_b, sink, scale, window, keep_first, static_cast<TT*>(out), ldo, H, G, D, \
-                E, tok_list)
-  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
-  else if (dtype == B200_F16) LAUNCH(__half);
-  else if (dtype == B200_F32) LAUNCH(float);
-  else B200_REQUIRE(false, "b200_sink_attn: dtype %d", dtype);
+                tok_pos, tok_b, sink, scale, window, keep_first, static_cast<TO*>(out), ldo, H, G, D, \
+                E, tok_list, softcap, ldo_plane)
+  if (all_values) {
+    if (dtype == B200_BF16) LAUNCH(__nv_bfloat16, float);
+    else if (dtype == B200_F16) LAUNCH(__half, float);
+    else if (dtype == B200_F32) LAUNCH(float, float);
+    else B200_REQUIRE(false, "b200_sink_attn: dtype %d", dtype);
+  } else {
+    if (dtype == B200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (dtype == B200_F16) LAUNCH(__half, __half);
+    else if (dtype == B200_F32) LAUNCH(float, float);
+    else B200_REQUIRE(false, "b200_sink_attn: dtype %d", dtype);
+  }
 #undef LAUNCH
   B200_CHECK_LAUNCH("sink_attn_kernel");
   return 0;
+}
+
+extern "C" int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int64_t ld_pool, int k_off,
+                              int v_off, const int* req_to_token, int64_t ld_r2t,
+                              const int64_t* req_idx, const int* tok_pos, const int* tok_b,
+                              const float* sink, float scale, int window, int keep_first, void* out,
+                              int64_t ldo, int T, int H, int G, int D, int E, const int* tok_list,
+                              int max_keys, int dtype, void* stream) {
+  return b200_sink_attn_heads(q, ldq, pool, ld_pool, k_off, v_off, req_to_token, ld_r2t, req_idx,
+                              tok_pos, tok_b, sink, scale, 0.f, window, keep_first, out, ldo, 0, 0, T, H,
+                              G, D, E, tok_list, max_keys, dtype, stream);
 }

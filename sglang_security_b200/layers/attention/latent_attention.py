@@ -20,7 +20,14 @@ Only c and kr are cached.  Two forms of the same sum run on them:
     64 or 128) on the tcgen05 extend kernel: (dim + rot_dim + vdim) instead of (2 R + rot_dim)
     multiply-adds per score.  16-bit engines only; chosen per step by a cost estimate.
 Both read the cache only, so a position's result does not depend on how the sequence was cut into
-steps or batched, beyond rounding."""
+steps or batched, beyond rounding.
+
+Variants, all parameters: `q_rank=None` projects the queries straight from h (no query latent and no
+norm of it): one fused GEMM [W_q ; W_dkv ; W_g]; `gate=True` multiplies the concatenated heads element
+by element with sigmoid(W_g h) before W_o; `rotary` replaces the default rotation by one with its own
+frequency table, pairing and sine/cosine multiplier (layers/rotary_embedding.py PairedRotary: a
+checkpoint in the half pairing has its rotated rows reordered as it is loaded, and the squared
+multiplier goes onto the cached key part)."""
 from __future__ import annotations
 
 import os
@@ -31,7 +38,7 @@ import torch.nn as nn
 
 from ... import _lib
 from ..linear import ColumnParallelLinear, RowParallelLinear
-from ..rotary_embedding import InterleavedRotary
+from ..rotary_embedding import InterleavedRotary, PairedRotary
 
 
 _SM_COUNT = 148      # B200
@@ -71,9 +78,10 @@ class LatentAttention(nn.Module):
     force_form: Optional[str] = None
 
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
-                 q_rank: int, scale: float, layer_id: int, eps: float, window: Optional[int] = None,
+                 q_rank: Optional[int], scale: float, layer_id: int, eps: float, window: Optional[int] = None,
                  rope_base: float = 10000.0, rope_dims: Optional[int] = None,
-                 kv_layer_id: Optional[int] = None, params_dtype: torch.dtype = torch.bfloat16):
+                 kv_layer_id: Optional[int] = None, params_dtype: torch.dtype = torch.bfloat16,
+                 rotary: Optional[PairedRotary] = None, gate: bool = False):
         super().__init__()
         self.width, self.heads, self.dim, self.rot_dim, self.vdim = width, heads, dim, rot_dim, vdim
         self.kv_rank, self.q_rank, self.scale, self.eps = kv_rank, q_rank, float(scale), eps
@@ -82,15 +90,30 @@ class LatentAttention(nn.Module):
         self.owns_kv = self.kv_layer_id == layer_id
         self.window = int(window) if window else 0
         kw = dict(bias=False, params_dtype=params_dtype, tp_rank=0, tp_size=1)
-        down_out = q_rank + (kv_rank + rot_dim if self.owns_kv else 0)
-        self.down_proj = ColumnParallelLinear(width, down_out, **kw)     # [W_dq ; W_dkv]
-        self.q_up_proj = ColumnParallelLinear(q_rank, heads * (dim + rot_dim), **kw)
+        self.gate = bool(gate)
+        q_out = heads * (dim + rot_dim)
+        # rows of the first GEMM: the query part (its latent, or the queries themselves), the KV latent
+        # and key part of a layer that owns them, the gate; padded to a multiple of 8
+        self.q_part = q_rank if q_rank is not None else q_out
+        self.kv_part = kv_rank + rot_dim if self.owns_kv else 0
+        self.gate_part = heads * vdim if gate else 0
+        down_out = self.q_part + self.kv_part + self.gate_part
+        if q_rank is None:
+            down_out = (down_out + 7) // 8 * 8
+        self.down_proj = ColumnParallelLinear(width, down_out, **kw)     # [W_dq or W_q ; W_dkv ; W_g]
+        if down_out != self.q_part + self.kv_part + self.gate_part:
+            self.down_proj.weight.data.zero_()
+        self.q_up_proj = ColumnParallelLinear(q_rank, q_out, **kw) if q_rank is not None else None
         self.o_proj = RowParallelLinear(heads * vdim, width, **kw)
         self.w_uk = nn.Parameter(torch.empty(heads, dim, kv_rank, dtype=params_dtype), requires_grad=False)
         self.w_uv_t = nn.Parameter(torch.empty(heads, kv_rank, vdim, dtype=params_dtype), requires_grad=False)
-        self.q_norm_weight = nn.Parameter(torch.ones(q_rank, dtype=torch.float32), requires_grad=False)
+        self.q_norm_weight = (nn.Parameter(torch.ones(q_rank, dtype=torch.float32), requires_grad=False)
+                              if q_rank is not None else None)
         self.kv_norm_weight = nn.Parameter(torch.ones(kv_rank, dtype=torch.float32), requires_grad=False)
-        self.rotary = InterleavedRotary(rot_dim if rope_dims is None else rope_dims, rope_base)
+        self.rotary = rotary if rotary is not None else InterleavedRotary(
+            rot_dim if rope_dims is None else rope_dims, rope_base)
+        # sine and cosine multiplied by m on the query and the key side: m^2 on the cached key part
+        self.rot_scale = float(getattr(self.rotary, "amplitude", 1.0)) ** 2
         if self.rotary.dims > rot_dim:
             raise ValueError("rotary dims exceed the rotated part of a head")
         need = max(dim + rot_dim, vdim)
@@ -101,6 +124,23 @@ class LatentAttention(nn.Module):
     def load_down(self, w_dq: torch.Tensor, w_dkv: Optional[torch.Tensor]) -> None:
         w = w_dq if w_dkv is None else torch.cat([w_dq, w_dkv], 0)
         self.down_proj.weight.data.copy_(w)
+
+    def load_direct(self, w_q: torch.Tensor, w_dkv: torch.Tensor, w_g: Optional[torch.Tensor]) -> None:
+        """Checkpoint tensors of the variant without a query latent: W_q [H * (dim + rot_dim), width],
+        W_dkv [kv_rank + rot_dim, width], W_g [H * vdim, width].  The rotated rows of every query head and
+        of the key part are taken in the rotation's row order (half pairing -> neighbours)."""
+        if self.q_up_proj is not None or not self.owns_kv:
+            raise ValueError("load_direct is for a layer that projects its queries directly and owns its latent")
+        H, dq = self.heads, self.dim + self.rot_dim
+        order = getattr(self.rotary, "row_order", lambda n: torch.arange(n))(self.rot_dim).to(w_q.device)
+        wq = w_q.view(H, dq, -1)
+        wq = torch.cat([wq[:, :self.dim], wq[:, self.dim:][:, order]], 1).reshape(H * dq, -1)
+        wkv = torch.cat([w_dkv[:self.kv_rank], w_dkv[self.kv_rank:][order]], 0)
+        dst = self.down_proj.weight.data
+        dst[:self.q_part].copy_(wq)
+        dst[self.q_part:self.q_part + self.kv_part].copy_(wkv)
+        if self.gate:
+            dst[self.q_part + self.kv_part:self.q_part + self.kv_part + self.gate_part].copy_(w_g)
 
     def load_uk(self, w: torch.Tensor) -> None:      # [H * dim, R]
         self.w_uk.data.copy_(w.view(self.heads, self.dim, self.kv_rank))
@@ -228,7 +268,7 @@ class LatentAttention(nn.Module):
             plan["ext_start"].data_ptr(), plan["bs"], plan["max_ext"], H, H, D, D, self.scale, 0.0, 1.0, 1,
             self.window, code, _lib.current_stream())
         _lib.check(rc, "b200_attn_extend_window")
-        return o_x[:, :, :self.vdim].reshape(t, H * self.vdim)
+        return o_x[:, :, :self.vdim]                                               # [t, H, vdim], strided
 
     def forward(self, h: torch.Tensor, forward_batch) -> torch.Tensor:
         fb = forward_batch
@@ -238,32 +278,47 @@ class LatentAttention(nn.Module):
         pool = fb.token_to_kv_pool
         cache = pool.get_kv_buffer(self.layer_id)
         raw, _ = self.down_proj(h)
-        cq = torch.empty((t, self.q_rank), dtype=h.dtype, device=h.device)
-        kv_raw = raw[:, self.q_rank:] if self.owns_kv else None
+        direct = self.q_up_proj is None
+        cq = None if direct else torch.empty((t, self.q_rank), dtype=h.dtype, device=h.device)
+        kv_raw = raw[:, self.q_part:] if self.owns_kv else None
         inv_freq = self.rotary.inv_freq
-        rc = lib.b200_latent_prep(
-            raw.data_ptr(), raw.stride(0), self.q_rank, self.q_norm_weight.data_ptr(), cq.data_ptr(),
-            cq.stride(0), _lib.ptr(kv_raw), raw.stride(0), self.kv_rank, self.rot_dim, self.rotary.dims,
+        rc = lib.b200_latent_prep_scaled(
+            None if direct else raw.data_ptr(), raw.stride(0), 0 if direct else self.q_rank,
+            _lib.ptr(self.q_norm_weight), _lib.ptr(cq), cq.stride(0) if cq is not None else 0,
+            _lib.ptr(kv_raw), raw.stride(0), self.kv_rank, self.rot_dim, self.rotary.dims,
             self.kv_norm_weight.data_ptr(), _lib.ptr(inv_freq), fb.tok_pos.data_ptr(),
-            fb.out_cache_loc.data_ptr(), cache.data_ptr(), cache.stride(0), float(self.eps), t, code,
-            _lib.current_stream())
+            fb.out_cache_loc.data_ptr(), cache.data_ptr(), cache.stride(0), float(self.eps), self.rot_scale, t,
+            code, _lib.current_stream())
         _lib.check(rc, "b200_latent_prep")
-        q, _ = self.q_up_proj(cq)
+        if direct:
+            q = raw[:, :self.q_part]
+        else:
+            q, _ = self.q_up_proj(cq)
         q3 = q.view(t, self.heads, self.dim + self.rot_dim)
         plan = self._expand_plan(fb) if h.dtype != torch.float32 else False
         if plan and plan["rest"] is None:
-            heads_out = self._forward_expanded(q3, cache, plan, fb)
+            heads3 = self._forward_expanded(q3, cache, plan, fb)
         else:
-            heads_out = self._forward_absorbed(q, q3, cache, fb, plan["rest"] if plan else None)
+            heads3 = self._forward_absorbed(q, q3, cache, fb, plan["rest"] if plan else None)
             if plan:                  # a divided step: long portions expanded, the rest absorbed
-                heads_out = torch.where(plan["tok_mask"][:, None], self._forward_expanded(q3, cache, plan, fb),
-                                        heads_out)
+                heads3 = torch.where(plan["tok_mask"][:, None, None], self._forward_expanded(q3, cache, plan, fb),
+                                     heads3)
+        # heads3: [t, H, vdim] in either memory order; gate and lay out token-major in one pass
+        if self.gate:
+            z = raw[:, self.q_part + self.kv_part:]
+            heads_out = torch.empty((t, self.heads * self.vdim), dtype=h.dtype, device=h.device)
+            rc = lib.b200_sigmoid_gate_mul(heads3.data_ptr(), heads3.stride(0), heads3.stride(1), z.data_ptr(),
+                                           z.stride(0), 0, heads_out.data_ptr(), heads_out.stride(0), t,
+                                           self.heads, self.vdim, code, _lib.current_stream())
+            _lib.check(rc, "b200_sigmoid_gate_mul")
+        else:
+            heads_out = heads3.reshape(t, self.heads * self.vdim)
         out, _ = self.o_proj(heads_out)
         return out
 
     def _forward_absorbed(self, q: torch.Tensor, q3: torch.Tensor, cache: torch.Tensor, fb, rest) -> torch.Tensor:
-        """-> [T, H * vdim].  `rest`: the batch entries to run (None: all); rows of other entries are
-        left for the caller to fill."""
+        """-> [T, H, vdim] (a view of the head-major product).  `rest`: the batch entries to run (None:
+        all); rows of other entries are left for the caller to fill."""
         lib = _lib.load()
         h, t, inv_freq = q, q.shape[0], self.rotary.inv_freq
         code = _lib.dtype_code(q.dtype)
@@ -292,5 +347,4 @@ class LatentAttention(nn.Module):
             o_lat.data_ptr(), o_lat.stride(1), o_lat.stride(0), splits, _lib.ptr(ws),
             ws.numel() if ws is not None else 0, code, _lib.current_stream())
         _lib.check(rc, "b200_latent_attn")
-        v = torch.bmm(o_lat, self.w_uv_t)                                          # [H, T, vdim]
-        return v.transpose(0, 1).reshape(t, self.heads * self.vdim)
+        return torch.bmm(o_lat, self.w_uv_t).transpose(0, 1)                       # [H, T, vdim] -> [T, H, vdim]

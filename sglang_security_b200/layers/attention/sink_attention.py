@@ -99,7 +99,10 @@ class SinkAttention(nn.Module):
                     "req": fb.req_pool_indices[dev[0]], "prefix": dev[1].to(torch.int32),
                     "ext": dev[2].to(torch.int32), "start": dev[3].to(torch.int32), "seq": dev[4].contiguous(),
                     "rest": (torch.tensor(rest, dtype=torch.int32).to(fb.req_pool_indices.device, non_blocking=True)
-                             if rest else None), "n_rest": len(rest)}
+                             if rest else None), "n_rest": len(rest),
+                    # (first row, rows) of the entries of either kind, for per-row steps that follow
+                    "ranges": [(starts[b], ext[b]) for b in long],
+                    "rest_ranges": [(starts[b], n) for b, n in enumerate(ext) if n < min_tokens]}
         fb.extra[key] = plan
         return plan
 

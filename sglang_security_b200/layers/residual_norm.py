@@ -5,7 +5,9 @@
     x += mult * y / sqrt(mean(y^2) + eps) * weight
 
 `AddNormed` owns the weight; one launch does the sum, the norm, the add and, on request, the copy of
-the new residual in the model dtype that the next sublayer's matrix products read.  `ResidualRMSNorm`
+the new residual in the model dtype that the next sublayer's matrix products read.  For designs with a
+norm BEFORE every sublayer as well, that copy is the next sublayer's pre-norm
+x / sqrt(mean(x^2) + eps) * next_weight instead (still the one launch).  `ResidualRMSNorm`
 is the plain RMS norm of the fp32 residual with a per-coordinate weight (a model's final norm), its
 output in the model dtype.  `softcap` is the logit cap cap * tanh(z / cap) with a fp32 result."""
 from __future__ import annotations
@@ -26,8 +28,10 @@ class AddNormed(nn.Module):
 
     def forward(self, x: torch.Tensor, a: Optional[torch.Tensor] = None, sa: float = 1.0,
                 b: Optional[torch.Tensor] = None, sb: float = 1.0, rows: Optional[torch.Tensor] = None,
-                top: int = 0, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
-        """x: fp32 residual [T, W], updated in place.  -> the new x in `out_dtype` (None: not asked)."""
+                top: int = 0, out_dtype: Optional[torch.dtype] = None,
+                next_weight: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """x: fp32 residual [T, W], updated in place.  -> the new x in `out_dtype` (None: not asked), or
+        with `next_weight` (fp32 [W]) its RMS norm times that weight."""
         if not x.is_cuda:
             raise _lib.B200Error("AddNormed: tensor must live on a CUDA device (no CPU path)")
         if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
@@ -41,17 +45,18 @@ class AddNormed(nn.Module):
                 raise _lib.B200Error("AddNormed: terms must share a dtype and have contiguous rows")
         t, w = x.shape
         out = None
-        if out_dtype is not None and out_dtype != torch.float32:
+        if out_dtype is not None and (out_dtype != torch.float32 or next_weight is not None):
             if out_dtype != dt:
                 raise _lib.B200Error("AddNormed: the copy of the residual has the terms' dtype")
             out = torch.empty((t, w), dtype=out_dtype, device=x.device)
         ld = lambda v: v.stride(0) if v is not None else 0
-        rc = _lib.load().b200_add_normed(
+        rc = _lib.load().b200_add_normed_next(
             x.data_ptr(), x.stride(0), _lib.ptr(a), ld(a), float(sa), _lib.ptr(b), ld(b), float(sb),
             _lib.ptr(rows), ld(rows), int(top), self.weight.data_ptr(), self.eps, self.mult,
-            _lib.ptr(out), ld(out), t, w, _lib.dtype_code(dt), _lib.current_stream())
+            _lib.ptr(out), ld(out), _lib.ptr(next_weight) if out is not None else None, t, w,
+            _lib.dtype_code(dt), _lib.current_stream())
         _lib.check(rc, "b200_add_normed")
-        return x if out_dtype == torch.float32 else out
+        return out if out is not None else (x if out_dtype == torch.float32 else None)
 
 
 class ResidualRMSNorm(nn.Module):

@@ -184,3 +184,59 @@ class InterleavedRotary(nn.Module):
         inv = torch.tensor([self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)],
                            dtype=torch.float64).to(torch.float32)
         self.register_buffer("inv_freq", inv, persistent=False)
+
+
+def ramp_scaled_frequencies(dims: int, base: float, factor: float, original: float, fast: float,
+                            slow: float):
+    """Frequency table of a rotation whose long wavelengths are stretched by `factor` and whose short
+    ones are kept, with a linear ramp between (YaRN: Peng et al., "YaRN: Efficient Context Window
+    Extension of Large Language Models").  With f_i = base^(-2i / dims) and
+        dim(t) = dims * ln(original / (2 pi t)) / (2 ln base)          (the pair that turns t times over
+                                                                        `original` positions)
+        lo = max(floor(dim(fast)), 0),  hi = min(ceil(dim(slow)), dims - 1)
+        ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+    pair i turns with f_i / factor * ramp_i + f_i * (1 - ramp_i), and sine and cosine are both
+    multiplied by 0.1 * ln(factor) + 1.  -> (fp64 frequencies [dims / 2], that multiplier)."""
+    if dims % 2:
+        raise ValueError("rotary dims must be even")
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+
+    def pair_of(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(pair_of(fast)), 0)
+    hi = min(math.ceil(pair_of(slow)), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / float(factor) * ramp + f * (1.0 - ramp), 0.1 * math.log(float(factor)) + 1.0
+
+
+class PairedRotary(InterleavedRotary):
+    """InterleavedRotary for checkpoints in either pairing, with an optional frequency table and a
+    multiplier on sine and cosine.  The kernels rotate neighbours (2i, 2i + 1).  A checkpoint in the
+    "half" pairing (i with i + dims / 2) is brought to that layout when it is loaded: `row_order` is
+    the order in which the rotated OUTPUT ROWS of a projection are taken, the same for the query and
+    the key side, so every score is unchanged.  `amplitude` multiplies sine and cosine on both sides;
+    kernels apply `amplitude ** 2` once, to the cached key part."""
+
+    def __init__(self, dims: int, base: float, pairing: str = "interleaved",
+                 frequencies: Optional[torch.Tensor] = None, amplitude: float = 1.0):
+        super().__init__(dims, base)
+        if pairing not in ("interleaved", "half"):
+            raise ValueError(f"unknown rotary pairing {pairing!r}")
+        self.pairing, self.amplitude = pairing, float(amplitude)
+        if frequencies is not None:
+            if frequencies.numel() != self.dims // 2:
+                raise ValueError("one frequency per rotated pair is expected")
+            self.inv_freq = frequencies.to(torch.float64).to(torch.float32)
+
+    def row_order(self, width: Optional[int] = None) -> torch.Tensor:
+        """Indices (into a rotated part of `width` >= dims coordinates) that bring a checkpoint's
+        rows to the interleaved layout; coordinates past `dims` keep their place."""
+        width = self.dims if width is None else int(width)
+        idx = torch.arange(width)
+        if self.pairing == "half":
+            half = self.dims // 2
+            idx[0:self.dims:2] = torch.arange(half)
+            idx[1:self.dims:2] = torch.arange(half) + half
+        return idx

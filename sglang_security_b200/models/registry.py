@@ -32,7 +32,7 @@ def register_model(architecture: str):
 
 
 def resolve_model_cls(architecture: str):
-    from . import desirax, dozetar  # noqa: F401  (register themselves)
+    from . import desirax, dozetar, kulesun  # noqa: F401  (register themselves)
 
     if architecture not in _MODELS:
         raise ValueError(f"architecture {architecture!r} is not supported; known: {sorted(_MODELS)}")
@@ -40,6 +40,6 @@ def resolve_model_cls(architecture: str):
 
 
 def supported_architectures():
-    from . import desirax, dozetar  # noqa: F401
+    from . import desirax, dozetar, kulesun  # noqa: F401
 
     return sorted(_MODELS)
