@@ -548,10 +548,11 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--arch-compare", default=None, metavar="SIZES",
-                    help="instead of the headline workload: prefill / decode throughput of the Desirax and "
-                         "Dozetar designs beside the Llama-family stack at equal size ('all' or comma-separated "
-                         "names of model_executor/arch_bench.py SIZES / DOZETAR_SIZES, e.g. dz-w1024,dz-w2048); "
-                         "one JSON line per model and size")
+                    help="instead of the headline workload: prefill / decode throughput of the Desirax, "
+                         "Dozetar and Kulesun designs beside the Llama-family stack at equal size ('all' or "
+                         "comma-separated names of model_executor/arch_bench.py SIZES / DOZETAR_SIZES / "
+                         "KULESUN_SIZES, e.g. dz-w1024,ku-w1024; a Kulesun size also runs the Desirax stack at "
+                         "equal size); one JSON line per model and size")
     args = ap.parse_args()
     if args.arch_compare:
         from sglang_security_b200 import build as _build

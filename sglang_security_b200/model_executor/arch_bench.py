@@ -1,7 +1,8 @@
-"""Prefill and decode throughput of the Desirax and Dozetar designs at layer sizes that resemble a real
-model's, beside the Llama-family decoder stack of this package at equal width / heads / head size /
+"""Prefill and decode throughput of the Desirax, Dozetar and Kulesun designs at layer sizes that resemble
+a real model's, beside the Llama-family decoder stack of this package at equal width / heads / head size /
 layer count and equal active feed-forward size (random weights, bf16).  Driven by
-`bench.py --arch-compare` (sizes named "dz-..." are Dozetar's).
+`bench.py --arch-compare` (sizes named "dz-..." are Dozetar's, "ku-..." Kulesun's; a Kulesun size also
+runs the Desirax stack, its closest relative, at equal width, heads, latent sizes, layers and feed-forward).
 
 Timing: CUDA events on the launching stream around whole engine steps, after warm-up steps; every step
 touches more weight and cache bytes than L2 holds at the larger size.  Per-kernel times come from the
@@ -35,6 +36,14 @@ DOZETAR_SIZES = {
     "dz-w2048": dict(width=2048, layers=4, vocab=32000, heads=16, kv_heads=4, dim=128, vdim=128, window=4096,
                      keep_first=4, rot=64, m_heads=16, m_dim=128, m_vdim=128, r_heads=16, r_dim=64, r_vdim=128,
                      experts=32, top=4, expert_ff=1024, ff=4096, rot_llama=0),
+}
+# Kulesun: layers alternate the talking-heads attention mixer and two latent-attention mixers; dense
+# silu feed-forward everywhere.  The latent sizes are those of the Desirax row it is compared with.
+KULESUN_SIZES = {
+    "ku-w1024": dict(width=1024, layers=4, vocab=32000, heads=8, kv_heads=2, adim=128, avdim=128, dim=64, rot=64,
+                     vdim=128, kv_rank=256, q_rank=384, window=1 << 20, ff=4096, moe=None, rot_llama=64),
+    "ku-w2048": dict(width=2048, layers=4, vocab=32000, heads=16, kv_heads=2, adim=128, avdim=128, dim=64, rot=64,
+                     vdim=128, kv_rank=512, q_rank=768, window=1 << 20, ff=8192, moe=None, rot_llama=64),
 }
 WORK = dict(prefill_reqs=4, prefill_len=2048, decode_bs=32, decode_ctx=2048)
 
@@ -285,6 +294,112 @@ def bench_dozetar(name, s, steps, warmup, device="cuda"):
     return row
 
 
+def _kulesun_cfg(s):
+    att = {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["adim"],
+                                          "vdim": s["avdim"], "scale": s["adim"] ** -0.5, "softcap": 30.0,
+                                          "q_temp": {"coef": 0.3, "every": 512}, "v_mix": True}}
+    lat = {"type": "latent_attention", "mixer": {
+        "heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot"], "vdim": s["vdim"], "kv_rank": s["kv_rank"],
+        "scale": (s["dim"] + s["rot"]) ** -0.5,
+        "rot": {"base": 5e5, "dims": s["rot"], "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}}
+    f = {"kind": "dense", "ff": s["ff"]}
+    return {"architecture": "Kulesun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "logit_scale": 1.0,
+            "layers": [dict(att if i % 3 == 0 else lat, mlp=f) for i in range(s["layers"])]}
+
+
+def bench_kulesun(name, s, steps, warmup, device="cuda"):
+    from ..configs.kulesun import kulesun_config
+    from ..managers.schedule_batch import Req, StepItem
+    from ..managers.scheduler import Scheduler
+    from ..models.registry import resolve_model_cls
+    from .model_runner import ModelRunner
+
+    cfg = kulesun_config(_kulesun_cfg(s))
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = resolve_model_cls("Kulesun")(cfg, params_dtype=torch.bfloat16)
+    for n_, p in model.named_parameters():
+        if n_.endswith("norm_weight") or ("norm" in n_ and n_.endswith(".weight")):
+            p.data.fill_(1.0)
+        elif n_.endswith("head_mix"):
+            p.data.copy_(torch.eye(p.shape[0], device=p.device) * 0.8 + 0.02)
+        elif n_.endswith("v_mix"):
+            p.data.fill_(0.3)
+        elif n_.endswith("bias"):
+            p.data.zero_()
+        else:
+            p.data.normal_(0, 0.02)
+    W = WORK
+    bs = max(W["prefill_reqs"], W["decode_bs"])
+    tokens = W["decode_bs"] * (W["decode_ctx"] + 64) + W["prefill_reqs"] * W["prefill_len"]
+    runner = ModelRunner(None, torch.bfloat16, max_total_tokens=tokens, max_running_requests=bs + 1,
+                         context_length=max(W["prefill_len"], W["decode_ctx"] + 64), device=device,
+                         model=model.eval(), model_config=SimpleNamespace(architecture="Kulesun", hf_config=cfg))
+    sched = Scheduler(runner)
+    g = torch.Generator().manual_seed(1)
+    rnd = lambda n: torch.randint(0, s["vocab"], (n,), generator=g).tolist()
+
+    def prefill():
+        reqs = [Req(rid=f"p{i}", input_ids=rnd(W["prefill_len"])) for i in range(W["prefill_reqs"])]
+        for r in reqs:
+            assert runner.admit(r)
+        sched.run_step([StepItem(r, r.input_ids, want=[len(r.input_ids) - 1]) for r in reqs])
+        for r in reqs:
+            runner.release(r)
+
+    names = ["sink_attn", "attn_extend", "qk_norm_rope_write", "head_mix_gate", "sigmoid_gate_mul", "latent_attn",
+             "latent_expand", "latent_prep", "add_normed", "act_and_mul", "scalar_rmsnorm_shift"]
+    row = {"arch": "kulesun", "size": name}
+    ms = _timed(prefill, steps, warmup)
+    ntok = W["prefill_reqs"] * W["prefill_len"]
+    row["prefill_ms"], row["prefill_tokens_per_s"] = round(ms, 3), round(ntok / ms * 1e3)
+    row["prefill_kernels"] = _kernel_times(prefill, names)
+    reqs = [Req(rid=f"d{i}", input_ids=rnd(W["decode_ctx"])) for i in range(W["decode_bs"])]
+    for r in reqs:
+        assert runner.admit(r)
+    for i in range(0, len(reqs), 4):
+        sched.run_step([StepItem(r, r.input_ids) for r in reqs[i:i + 4]])
+    state = {"n": 0}
+
+    def decode():
+        state["n"] += 1
+        assert state["n"] < 60
+        sched.run_step([StepItem(r, [7], want=[0]) for r in reqs])
+
+    ms = _timed(decode, steps, warmup)
+    row["decode_ms"], row["decode_tokens_per_s"] = round(ms, 3), round(W["decode_bs"] / ms * 1e3)
+    row["decode_kernels"] = _kernel_times(decode, names)
+
+    def mixed():
+        state["n"] += 1
+        assert state["n"] < 60
+        new = Req(rid=f"m{state['n']}", input_ids=rnd(512))
+        assert runner.admit(new)
+        sched.run_step([StepItem(r, [7], want=[0]) for r in reqs] + [StepItem(new, new.input_ids, want=[511])])
+        runner.release(new)
+
+    row["mixed_ms"] = round(_timed(mixed, min(steps, 8), 3), 3)
+    # algorithmic work of one attention layer, all tokens.  Heads' weights mixed after the softmax: the
+    # cheapest exact one-pass form scores every pair once and applies every head's weights to the values of
+    # each of the G key/value heads (2 * pairs * H * (D + G * E)); what runs is one launch per value head
+    L, U, H, G, D, E = W["prefill_len"], W["prefill_reqs"], s["heads"], s["kv_heads"], s["adim"], s["avdim"]
+    pairs = U * (L * (L + 1) // 2)
+    row["attn_prefill_flops_needed"] = 2 * pairs * H * (D + G * E)
+    row["attn_prefill_flops_run"] = 2 * pairs * H * G * (D + E)
+    row["attn_layers"] = sum(1 for x in cfg.layers if x.type == "attention")
+    keys_d = W["decode_bs"] * (W["decode_ctx"] + 1)
+    row["attn_decode_bytes"] = keys_d * G * (D + E) * 2
+    R, rot = s["kv_rank"], s["rot"]
+    row["latent_attn_prefill_flops"] = 2 * pairs * H * (2 * R + rot)
+    d_exp = 64 if max(s["dim"] + rot, s["vdim"]) <= 64 else 128
+    row["expanded_attn_prefill_flops"] = 2 * pairs * H * 2 * d_exp
+    row["latent_attn_decode_bytes"] = keys_d * (R + rot) * 2
+    del runner, sched, model
+    torch.cuda.empty_cache()
+    return row
+
+
 def bench_llama_like(name, s, steps, warmup, device="cuda"):
     """The package's Llama-family stack (B200DecoderLayer: fused RMSNorm, rotary + KV write, paged
     attention, gated silu MLP) at the same width, heads, head size 128, layers, GQA 4:1, bf16."""
@@ -347,10 +462,14 @@ def bench_llama_like(name, s, steps, warmup, device="cuda"):
 
 def run(steps: int, warmup: int, sizes=None):
     rows = []
-    for name, s in list(SIZES.items()) + list(DOZETAR_SIZES.items()):
+    for name, s in list(SIZES.items()) + list(DOZETAR_SIZES.items()) + list(KULESUN_SIZES.items()):
         if sizes and name not in sizes:
             continue
-        for fn in ((bench_dozetar if name in DOZETAR_SIZES else bench_desirax), bench_llama_like):
+        if name in KULESUN_SIZES:
+            fns = (bench_kulesun, bench_desirax, bench_llama_like)
+        else:
+            fns = ((bench_dozetar if name in DOZETAR_SIZES else bench_desirax), bench_llama_like)
+        for fn in fns:
             t0 = time.time()
             row = fn(name, s, steps, warmup)
             row["wall_s"] = round(time.time() - t0, 1)
