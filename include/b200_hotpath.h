@@ -673,7 +673,8 @@ int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int64_t ld_poo
 
 /* b200_attn_extend_sink with one more option: v_head >= 0 makes every query head read the VALUES of
  * key/value head v_head while its keys stay those of its own key/value head (v_head < 0: its own).
- * Logit capping and a sink may be combined.                                                        */
+ * n_values 2: value heads v_head and v_head + 1 in one launch (scores and softmax once, two products);
+ * the second product goes o_plane elements behind the first.  Logit capping and a sink may be combined. */
 int b200_attn_extend_heads(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                            int64_t kv_row_stride, void* o, int64_t o_stride,
                            const int32_t* req_to_token, int64_t req_to_token_stride,
@@ -681,8 +682,8 @@ int b200_attn_extend_heads(const void* q, int64_t q_stride, const void* k_cache,
                            const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
                            const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq, int Hkv,
                            int D, int Dv, float scale, float logit_cap, float out_scale, int causal,
-                           int window, int keep_first, const float* sink, int v_head, int dtype,
-                           void* stream);
+                           int window, int keep_first, const float* sink, int v_head, int n_values,
+                           int64_t o_plane, int dtype, void* stream);
 /* b200_qk_norm_rope_write with the further options: queries times 1 + temp_coef * ln(floor((p + 1) /
  * temp_every) + 1) (temp_every 0: none); v_norm != 0: every value head divided by its root mean square
  * (eps, no weight); first_pool given: v <- (1 - *v_mix) v + *v_mix * first_pool[loc[t]][first_off ...]

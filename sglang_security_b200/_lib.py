@@ -216,7 +216,7 @@ _SIGNATURES = {
                                        c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_float, c_float, c_float, c_int, c_int, c_int, c_void_p, c_int,
-                                       c_int, c_void_p]),
+                                       c_int, c_int64, c_int, c_void_p]),
     "b200_qkv_prep_write": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                     c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
                                     c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,

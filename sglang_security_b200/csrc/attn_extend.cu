@@ -52,6 +52,8 @@ struct ExtendParams {
   const float* sink;             // [Hq] or NULL: exp(sink[h]) joins the softmax denominator, no key or value
   int v_head;                    // >= 0: every query head reads the values of this key/value head (keys
                                  // stay those of its own); < 0: its own key/value head's
+  int64_t o_plane;               // NV > 1 (value heads v_head .. v_head + NV - 1 in one launch: one score
+                                 // and softmax pass, NV products): elements between their output planes
 };
 
 constexpr int kExtThreads = 256;
@@ -59,7 +61,7 @@ constexpr int kKvTile = 64;
 constexpr int kLoaders = 96;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
-template <int D>
+template <int D, int NV = 1>
 struct ExtendCfg {
   static constexpr int PANELS = D / 64;                 // 128-byte-wide panels per row
   static constexpr int Q_BYTES = 128 * D * 2;
@@ -67,11 +69,13 @@ struct ExtendCfg {
   static constexpr int P_BYTES = 128 * kKvTile * 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = Q_BYTES;                  // 2 stages
-  static constexpr int OFF_V = OFF_K + 2 * KV_TILE_BYTES;
-  static constexpr int OFF_P = OFF_V + 2 * KV_TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + 2 * KV_TILE_BYTES; // 2 stages of NV value tiles
+  static constexpr int V_STAGE_BYTES = NV * KV_TILE_BYTES;
+  static constexpr int OFF_P = OFF_V + 2 * V_STAGE_BYTES;
   static constexpr int OFF_BAR = OFF_P + P_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 128;
-  static constexpr int TMEM_COLS = D == 128 ? 256 : 128;  // S: 64 cols, O: D cols
+  static constexpr int TMEM_COLS = 64 + NV * D <= 128 ? 128 : (64 + NV * D <= 256 ? 256 : 512);  // S: 64 cols, O: NV * D
+  static_assert(64 + NV * D <= 512, "accumulators exceed tensor memory");
   static constexpr int O_COL = 64;
 };
 
@@ -97,10 +101,10 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 // packed FFMA2 per two elements (exp2(s * scale - m)), and the row sum accumulates with FFMA2.
 // Same values up to fp32 rounding of the fused multiply-add.  Not used with logit capping or a
 // non-positive scale (dispatch falls back to the FAST = false instance, unchanged from round 1).
-template <typename T, int D, bool FAST = false>
+template <typename T, int D, bool FAST = false, int NV = 1>
 __global__ void __launch_bounds__(kExtThreads, 2)
 attn_extend_kernel(const ExtendParams p) {
-  using C = ExtendCfg<D>;
+  using C = ExtendCfg<D, NV>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   if ((sbase & 1023u) != 0) __trap();  // swizzled operands need a 1024-byte aligned base
@@ -197,7 +201,7 @@ attn_extend_kernel(const ExtendParams p) {
     auto issue_tile = [&](int j) {
       const int stage = j & 1;
       const uint32_t sk = sbase + C::OFF_K + stage * C::KV_TILE_BYTES;
-      const uint32_t sv = sbase + C::OFF_V + stage * C::KV_TILE_BYTES;
+      const uint32_t sv = sbase + C::OFF_V + stage * C::V_STAGE_BYTES;
 #pragma unroll
       for (int i = 0; i < PASSES; ++i) {
         const int r = lrow + RPP * i;
@@ -205,7 +209,9 @@ attn_extend_kernel(const ExtendParams p) {
           const int64_t off = static_cast<int64_t>(slots[i]) * row_bytes + lcol * 16;
           const uint32_t so = swz_off<kKvTile>(r, lcol);
           cp_async16(sk + so, kbase + off);
-          cp_async16(sv + so, vbase + off);
+#pragma unroll
+          for (int vh = 0; vh < NV; ++vh)
+            cp_async16(sv + vh * C::KV_TILE_BYTES + so, vbase + off + static_cast<int64_t>(vh) * D * 2);
         }
       }
       cp_async_commit();
@@ -258,14 +264,17 @@ attn_extend_kernel(const ExtendParams p) {
         }
         tc::mbar_wait(bar_p_full, j & 1u);
         tc::tc_fence_after();
-        const uint32_t sv = sbase + C::OFF_V + (j & 1) * C::KV_TILE_BYTES;
+        const uint32_t sv = sbase + C::OFF_V + (j & 1) * C::V_STAGE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < kKvTile / 16; ++kk) {
-          // A = P [128 x 64 tokens], K-major; B = V rows kk*16.., MN-major: LBO = panel stride
-          tc::mma_f16(tmem_o, tc::make_smem_desc_sw128(sbase + C::OFF_P + kk * 32, 1024, 16),
-                      tc::make_smem_desc_sw128(sv + kk * 16 * 128, 1024, kKvTile * 128), idesc_pv,
-                      (j | kk) != 0 ? 1u : 0u);
-        }
+        for (int vh = 0; vh < NV; ++vh)
+#pragma unroll
+          for (int kk = 0; kk < kKvTile / 16; ++kk) {
+            // A = P [128 x 64 tokens], K-major; B = V rows kk*16.., MN-major: LBO = panel stride
+            tc::mma_f16(tmem_o + vh * D, tc::make_smem_desc_sw128(sbase + C::OFF_P + kk * 32, 1024, 16),
+                        tc::make_smem_desc_sw128(sv + vh * C::KV_TILE_BYTES + kk * 16 * 128, 1024,
+                                                 kKvTile * 128),
+                        idesc_pv, (j | kk) != 0 ? 1u : 0u);
+          }
         tc::mma_commit(bar_pv_full);
         tc::mma_commit(bar_kv_empty(j & 1));
       }
@@ -350,7 +359,7 @@ attn_extend_kernel(const ExtendParams p) {
           pv_waited = true;
           const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
 #pragma unroll 1
-          for (int cc = 0; cc < D / 32; ++cc) {
+          for (int cc = 0; cc < NV * D / 32; ++cc) {
             uint32_t o[32];
             tc::tmem_ld32(tmem_o + cc * 32, o);
             tc::tmem_ld_wait();
@@ -422,9 +431,11 @@ attn_extend_kernel(const ExtendParams p) {
     T* orow = static_cast<T*>(p.o) + (q_row0 + (row_ok ? tok : 0)) * p.o_stride +
               static_cast<int64_t>(head_base + r % p.pack) * D;
 #pragma unroll 1
-    for (int cc = 0; cc < D / 32; ++cc) {
+    for (int cv = 0; cv < NV * D / 32; ++cv) {
+      const int vh = cv / (D / 32), cc = cv - vh * (D / 32);
+      T* orow_v = orow + vh * p.o_plane;
       uint32_t v[32];
-      tc::tmem_ld32(tmem_o + cc * 32, v);
+      tc::tmem_ld32(tmem_o + cv * 32, v);
       tc::tmem_ld_wait();
       if (row_ok) {
 #pragma unroll
@@ -442,7 +453,7 @@ attn_extend_kernel(const ExtendParams p) {
               w[e] = *reinterpret_cast<uint32_t*>(&t2);
             }
           }
-          *reinterpret_cast<uint4*>(orow + cc * 32 + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(orow_v + cc * 32 + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }
@@ -459,10 +470,11 @@ static bool extend_fast_softmax_enabled() {
   return !(e && e[0] == '0');
 }
 
-template <typename T, int D, bool FAST>
+template <typename T, int D, bool FAST, int NV = 1>
 static int launch_extend_inst(const ExtendParams& p, int bs, int max_extend_len, cudaStream_t st) {
-  using C = ExtendCfg<D>;
-  auto kern = attn_extend_kernel<T, D, FAST>;
+  using C = ExtendCfg<D, NV>;
+  static_assert(C::SMEM_BYTES <= 227 * 1024, "tiles exceed shared memory");
+  auto kern = attn_extend_kernel<T, D, FAST, NV>;
   static bool attr_done = false;
   if (!attr_done) {
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -480,9 +492,12 @@ static int launch_extend_inst(const ExtendParams& p, int bs, int max_extend_len,
 }
 
 template <typename T, int D>
-static int launch_extend(const ExtendParams& p, int bs, int max_extend_len, cudaStream_t st) {
+static int launch_extend(const ExtendParams& p, int n_values, int bs, int max_extend_len, cudaStream_t st) {
   const bool fast = p.logit_cap <= 0.f && p.qk_scale > 0.f && extend_fast_softmax_enabled();
-  note_variant("attn_extend d=%d fast_softmax=%d", D, fast ? 1 : 0);
+  note_variant("attn_extend d=%d fast_softmax=%d values=%d", D, fast ? 1 : 0, n_values);
+  if (n_values == 2)
+    return fast ? launch_extend_inst<T, D, true, 2>(p, bs, max_extend_len, st)
+                : launch_extend_inst<T, D, false, 2>(p, bs, max_extend_len, st);
   return fast ? launch_extend_inst<T, D, true>(p, bs, max_extend_len, st)
               : launch_extend_inst<T, D, false>(p, bs, max_extend_len, st);
 }
@@ -546,7 +561,7 @@ int b200_attn_extend_sink(const void* q, int64_t q_stride, const void* k_cache, 
   return b200_attn_extend_heads(q, q_stride, k_cache, v_cache, kv_row_stride, o, o_stride, req_to_token,
                                 req_to_token_stride, req_pool_indices, seq_lens, extend_prefix_lens,
                                 extend_seq_lens, extend_start_loc, bs, max_extend_len, Hq, Hkv, D, Dv,
-                                scale, logit_cap, out_scale, causal, window, keep_first, sink, -1, dtype,
+                                scale, logit_cap, out_scale, causal, window, keep_first, sink, -1, 1, 0, dtype,
                                 stream);
 }
 
@@ -557,11 +572,13 @@ int b200_attn_extend_heads(const void* q, int64_t q_stride, const void* k_cache,
                            const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
                            const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq, int Hkv,
                            int D, int Dv, float scale, float logit_cap, float out_scale, int causal,
-                           int window, int keep_first, const float* sink, int v_head, int dtype,
-                           void* stream) {
+                           int window, int keep_first, const float* sink, int v_head, int n_values,
+                           int64_t o_plane, int dtype, void* stream) {
   using namespace b200;
   B200_REQUIRE(keep_first >= 0 && v_head < Hkv, "b200_attn_extend: kept tokens %d, value head %d",
                keep_first, v_head);
+  B200_REQUIRE(n_values == 1 || (n_values == 2 && v_head >= 0 && v_head + 2 <= Hkv && o_plane % 8 == 0),
+               "b200_attn_extend: %d value heads from %d in one launch", n_values, v_head);
   B200_REQUIRE(window >= 0 && (window == 0 || causal), "b200_attn_extend: a window needs causal");
   if (bs == 0 || max_extend_len == 0) return 0;
   B200_REQUIRE(q && k_cache && v_cache && o && req_to_token && req_pool_indices && seq_lens &&
@@ -607,13 +624,14 @@ int b200_attn_extend_heads(const void* q, int64_t q_stride, const void* k_cache,
   p.keep_first = window > 0 ? keep_first : 0;
   p.sink = sink;
   p.v_head = v_head;
+  p.o_plane = o_plane;
   B200_REQUIRE(bs <= 65535 && Hkv * p.head_tiles <= 65535, "b200_attn_extend: grid too large");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == B200_BF16)
-    return D == 128 ? launch_extend<__nv_bfloat16, 128>(p, bs, max_extend_len, st)
-                    : launch_extend<__nv_bfloat16, 64>(p, bs, max_extend_len, st);
-  return D == 128 ? launch_extend<__half, 128>(p, bs, max_extend_len, st)
-                  : launch_extend<__half, 64>(p, bs, max_extend_len, st);
+    return D == 128 ? launch_extend<__nv_bfloat16, 128>(p, n_values, bs, max_extend_len, st)
+                    : launch_extend<__nv_bfloat16, 64>(p, n_values, bs, max_extend_len, st);
+  return D == 128 ? launch_extend<__half, 128>(p, n_values, bs, max_extend_len, st)
+                  : launch_extend<__half, 64>(p, n_values, bs, max_extend_len, st);
 }
 
 }  // extern "C"

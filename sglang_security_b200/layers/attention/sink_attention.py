@@ -77,6 +77,17 @@ class SinkAttention(nn.Module):
                 and self.tensor_core_min_tokens > 0)
 
     @staticmethod
+    def _merged(ranges):
+        """(first row, rows) ranges in row order, neighbours joined."""
+        out = []
+        for start, n in ranges:
+            if out and out[-1][0] + out[-1][1] == start:
+                out[-1] = (out[-1][0], out[-1][1] + n)
+            else:
+                out.append((start, n))
+        return out
+
+    @staticmethod
     def _plan(fb, min_tokens: int):
         """Which batch entries take the tensor-core kernel: their sub-tables (one host-to-device copy),
         and the rows of all other tokens.  Shared by the layers of a step."""
@@ -101,8 +112,9 @@ class SinkAttention(nn.Module):
                     "rest": (torch.tensor(rest, dtype=torch.int32).to(fb.req_pool_indices.device, non_blocking=True)
                              if rest else None), "n_rest": len(rest),
                     # (first row, rows) of the entries of either kind, for per-row steps that follow
-                    "ranges": [(starts[b], ext[b]) for b in long],
-                    "rest_ranges": [(starts[b], n) for b, n in enumerate(ext) if n < min_tokens]}
+                    "ranges": SinkAttention._merged([(starts[b], ext[b]) for b in long]),
+                    "rest_ranges": SinkAttention._merged([(starts[b], n) for b, n in enumerate(ext)
+                                                          if n < min_tokens])}
         fb.extra[key] = plan
         return plan
 

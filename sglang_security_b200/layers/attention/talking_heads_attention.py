@@ -15,7 +15,8 @@ The mixed output is linear in the weights: out_h = sum_g M[h, g] A[c(h)][g] with
 w_g(i, j) v_c(j), so the attention kernels run their usual one-pass softmax once per VALUE head (every
 query head's weights on that head's values) and csrc/head_mix.cu combines the planes per token and
 applies the gate.  Prompt portions of at least `tensor_core_min_tokens` tokens run on the tcgen05 extend
-kernel (16-bit operands, fp32 scores, maxima and sums; key and value size equal, 64 or 128), decoded
+kernel (16-bit operands, fp32 scores, maxima and sums; key and value size equal, 64 or 128; two value
+heads per launch share one pass of scores and softmax, each with its own accumulator), decoded
 tokens and short portions on the CUDA-core kernel (fp32 throughout; the only path of a 32-bit engine).
 Both read the pool only, so a position's result does not depend on how the prompt was cut or batched
 beyond rounding.  Every option is a parameter; without temperature, cap, mix and gate this is plain
@@ -126,13 +127,15 @@ class TalkingHeadsAttention(nn.Module):
                 self._mix(planes, z, out, start, n, code, st)
         if plan is not None:
             planes16 = torch.empty((G, T, H * E), dtype=h.dtype, device=h.device)
-            for gv in range(G):
+            for gv in range(0, G, 2):           # two value heads per launch: scores and softmax once
+                pair = 2 if gv + 1 < G else 1
                 rc = lib.b200_attn_extend_heads(
                     q16.data_ptr(), q16.stride(0), pool.data_ptr(), pool[:, G * D:].data_ptr(), pool.stride(0),
                     planes16[gv].data_ptr(), planes16.stride(1), r2t.data_ptr(), r2t.stride(0),
                     plan["req"].data_ptr(), plan["seq"].data_ptr(), plan["prefix"].data_ptr(),
                     plan["ext"].data_ptr(), plan["start"].data_ptr(), plan["bs"], plan["max_ext"], H, G, D, E,
-                    self.scale, self.softcap, 1.0, 1, 0, 0, _lib.ptr(self.sink), gv if G > 1 else -1, code, st)
+                    self.scale, self.softcap, 1.0, 1, 0, 0, _lib.ptr(self.sink), gv if G > 1 else -1, pair,
+                    planes16.stride(0), code, st)
                 _lib.check(rc, "b200_attn_extend_heads")
             for start, n in plan["ranges"]:
                 self._mix(planes16, z, out, start, n, code, st)
