@@ -117,7 +117,9 @@ attn_extend_kernel(const ExtendParams p) {
   const int ext = p.extend_lens[b];
   const int prefix = p.prefix_lens[b];
   const int tok_per_tile = 128 / p.pack;
-  const int tok0 = blockIdx.x * tok_per_tile;
+  // causal rows see more keys the later they are: the last query tiles are launched first, so the
+  // longest CTAs do not form the tail of the grid
+  const int tok0 = static_cast<int>(gridDim.x - 1 - blockIdx.x) * tok_per_tile;
   if (tok0 >= ext) return;  // uniform for the CTA
   const int kvh = blockIdx.y / p.head_tiles;
   const int head_base = kvh * p.group + (blockIdx.y - kvh * p.head_tiles) * p.pack;
