@@ -18,6 +18,11 @@ constexpr int kMixThreads = 256;
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
+// A thread owns one value column e of one plane c and forms the outputs of that plane's R = H / G heads,
+// kMixHeads at a time: the H inputs a[g][e] are loaded once per kMixHeads outputs (coalesced over e),
+// the mix row comes from shared memory as a broadcast.
+constexpr int kMixHeads = 8;
+
 template <typename TA, typename T>
 __global__ void __launch_bounds__(kMixThreads)
 head_mix_gate_kernel(const TA* __restrict__ a, int64_t lda, int64_t lda_plane,
@@ -31,13 +36,30 @@ head_mix_gate_kernel(const TA* __restrict__ a, int64_t lda, int64_t lda_plane,
   }
   const float* m = in_smem ? mix_s : mix;
   const int t = blockIdx.x, R = H / G;
-  for (int i = threadIdx.x; i < H * E; i += kMixThreads) {
-    const int h = i / E, e = i - h * E;
-    const TA* row = a + static_cast<int64_t>(h / R) * lda_plane + t * lda + e;
-    float o = 0.f;
-    for (int g = 0; g < H; ++g) o = fmaf(m[h * H + g], to_float<TA>(row[g * E]), o);
-    if (gate) o *= sigmoidf_(to_float<T>(gate[t * ldg + h]));
-    out[t * ldo + i] = from_float<T>(o);
+  for (int i = threadIdx.x; i < G * E; i += kMixThreads) {
+    const int c = i / E, e = i - c * E;
+    const TA* col = a + static_cast<int64_t>(c) * lda_plane + t * lda + e;
+    for (int h0 = c * R; h0 < (c + 1) * R; h0 += kMixHeads) {
+      const int nh = min(kMixHeads, (c + 1) * R - h0);
+      float acc[kMixHeads];
+#pragma unroll
+      for (int r = 0; r < kMixHeads; ++r) acc[r] = 0.f;
+#pragma unroll 8                              // eight loads in flight per thread: the kernel is bound by
+      for (int g = 0; g < H; ++g) {                // bytes in flight, not by arithmetic
+        const float x = to_float<TA>(col[g * E]);
+#pragma unroll
+        for (int r = 0; r < kMixHeads; ++r)
+          if (r < nh) acc[r] = fmaf(m[(h0 + r) * H + g], x, acc[r]);
+      }
+#pragma unroll
+      for (int r = 0; r < kMixHeads; ++r) {
+        if (r < nh) {
+          float o = acc[r];
+          if (gate) o *= sigmoidf_(to_float<T>(gate[t * ldg + h0 + r]));
+          out[t * ldo + (h0 + r) * E + e] = from_float<T>(o);
+        }
+      }
+    }
   }
 }
 
