@@ -294,7 +294,13 @@ attn_extend_kernel(const ExtendParams p) {
     const bool capped = p.logit_cap > 0.f;
     const float inv_cap = capped ? 1.f / p.logit_cap : 0.f;
     const float cap_log2 = p.logit_cap * 1.4426950408889634f;
-    float m = -INFINITY, l = 0.f;
+    // FAST with a cap: a capped score never exceeds the cap, so the cap itself is the reference of every
+    // exponent: exp2(s - cap) = exp2(-2 cap / (e^(2x) + 1)) with x = raw * scale / cap.  No running
+    // maximum, no rescaling of O, one pass over the tile (the host takes this form for caps whose
+    // e^(-2 cap) stays a normal number)
+    const bool lean_cap = FAST && capped;
+    const float cap_k1 = p.qk_scale * inv_cap * 2.8853900817779268f, cap_k2 = -2.0f * cap_log2;
+    float m = lean_cap ? cap_log2 : -INFINITY, l = 0.f;
 
     auto score = [&](uint32_t raw, int kpos) -> float {
       float s = __uint_as_float(raw) * p.qk_scale;
@@ -319,9 +325,12 @@ attn_extend_kernel(const ExtendParams p) {
       tc::tc_fence_before();
       tc::mbar_arrive(bar_s_free);
       float mt = -INFINITY;
-      if constexpr (FAST) {
-        const int k0 = tile_of(j) * kKvTile;
-        if (k0 + kKvTile - 1 > limit || k0 < first) {  // the tile crosses an edge of this row's visible keys
+      const int k0 = tile_of(j) * kKvTile;
+      const bool edge = k0 + kKvTile - 1 > limit || k0 < first;  // the tile crosses an edge of this row's keys
+      if (lean_cap) {
+        // nothing to find: m is the cap
+      } else if constexpr (FAST) {
+        if (edge) {
 #pragma unroll
           for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -385,7 +394,18 @@ attn_extend_kernel(const ExtendParams p) {
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
           float p0, p1;
-          if constexpr (FAST) {
+          if (lean_cap) {
+            const float e0 = fast_exp2(__uint_as_float(v[h][2 * c]) * cap_k1);
+            const float e1 = fast_exp2(__uint_as_float(v[h][2 * c + 1]) * cap_k1);
+            p0 = fast_exp2(__fdividef(cap_k2, e0 + 1.0f));
+            p1 = fast_exp2(__fdividef(cap_k2, e1 + 1.0f));
+            if (edge) {
+              const int kp = k0 + h * 32 + 2 * c;
+              if (kp > limit || (kp < first && kp >= kept)) p0 = 0.f;
+              if (kp + 1 > limit || (kp + 1 < first && kp + 1 >= kept)) p1 = 0.f;
+            }
+            lsum = ffma2(make_float2(p0, p1), one2, lsum);
+          } else if constexpr (FAST) {
             const float2 x = ffma2(make_float2(__uint_as_float(v[h][2 * c]),
                                                __uint_as_float(v[h][2 * c + 1])), sc2, nm2);
             p0 = fast_exp2(x.x);
@@ -495,7 +515,8 @@ static int launch_extend_inst(const ExtendParams& p, int bs, int max_extend_len,
 
 template <typename T, int D>
 static int launch_extend(const ExtendParams& p, int n_values, int bs, int max_extend_len, cudaStream_t st) {
-  const bool fast = p.logit_cap <= 0.f && p.qk_scale > 0.f && extend_fast_softmax_enabled();
+  // a cap up to 40 keeps e^(-2 cap) a normal fp32 (and 16-bit) number: the one-pass capped form
+  const bool fast = p.logit_cap <= 40.f && p.qk_scale > 0.f && extend_fast_softmax_enabled();
   note_variant("attn_extend d=%d fast_softmax=%d values=%d", D, fast ? 1 : 0, n_values);
   if (n_values == 2)
     return fast ? launch_extend_inst<T, D, true, 2>(p, bs, max_extend_len, st)

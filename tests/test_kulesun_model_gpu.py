@@ -29,13 +29,16 @@ CONFIGS = {
                            (U.attention(heads=1, kv_heads=1, dim=6, vdim=11, every=2, coef=2.0), None)],
                           vocab=53, width=27, eps=1e-4, embed_scale=2.0, logit_scale=0.05),
     # sizes the tensor-core kernels take: attention key size = value size = 64 grouped 2 : 1 and 128
-    # ungrouped (two value heads per launch), three key/value heads (a pair and a single one), latent heads
-    # that expand to 64
+    # (two value heads per launch; capped in the one-pass form and uncapped), three key/value heads (a pair
+    # and a single one) with a cap too large for the one-pass form, one key/value head, latent heads that
+    # expand to 64
     "d": lambda: U.config([(U.attention(heads=4, kv_heads=2, dim=64, vdim=64, every=40), U.dense(64)),
                            (U.latent(heads=2, dim=32, rot_dim=32, vdim=32, kv_rank=64), None),
-                           (U.attention(heads=4, kv_heads=2, dim=64, vdim=64, every=64), None),
+                           (U.attention(heads=4, kv_heads=2, dim=64, vdim=64, every=64, softcap=None), None),
                            (U.attention(heads=2, kv_heads=2, dim=128, vdim=128, v_mix=False, softcap=None), U.dense(64)),
-                           (U.attention(heads=6, kv_heads=3, dim=64, vdim=64, v_mix=False, every=0), None)],
+                           (U.attention(heads=4, kv_heads=2, dim=128, vdim=128, v_mix=False, softcap=25.0), None),
+                           (U.attention(heads=6, kv_heads=3, dim=64, vdim=64, v_mix=False, every=0, softcap=60.0), None),
+                           (U.attention(heads=2, kv_heads=1, dim=64, vdim=64, v_mix=False, softcap=8.0), None)],
                           vocab=101, width=64),
     # attention only, no layer mixes values; latent only
     "e": lambda: U.config([(U.attention(v_mix=False), None), (U.attention(heads=2, kv_heads=2, v_mix=False), U.dense())],
