@@ -730,6 +730,84 @@ int b200_latent_prep_scaled(const void* qraw, int64_t ldq, int QR, const float* 
                             const int64_t* loc, void* cache, int64_t ldc, float eps, float rot_scale,
                             int T, int dtype, void* stream);
 
+/* Norm AFTER the residual sum, with weight and bias: y = alpha * x + a + b + sum_k wts[t, k] *
+ * rows[t * top + k] (terms optional, wts NULL = 1) in fp32; x <- (y - mean) / sqrt(var + eps) * w + bias
+ * (var = mean of the squared deviations); out_h (optional) = the new x in out_dtype (the terms' dtype or
+ * fp32).  in_place = 0: x is only read (a final norm; out_h required).                              */
+int b200_scaled_add_layernorm(float* x, int64_t ldx, float alpha, const void* a, int64_t lda,
+                              const void* b, int64_t ldb, const void* rows, int64_t ld_rows,
+                              const float* wts, int top, const float* w, const float* bias, float eps,
+                              void* out_h, int64_t ldh, int in_place, int T, int W, int dtype,
+                              int out_dtype, void* stream);
+/* out[t, d] = g * sigmoid(slope * g) * (u + 1), g = min(z[t, d], limit), u = clamp(z[t, D + d], +-limit). */
+int b200_act_and_mul_clamped(const void* z, int64_t ldz, void* out, int64_t ldo, int T, int D,
+                             float limit, float slope, int dtype, void* stream);
+/* b200_gated_group_rmsnorm with the gate's form as an argument: 0 = sigmoid(z) after the norm,
+ * 1 = silu(z) multiplied BEFORE the norm (the norm sees the gated values).                          */
+int b200_gated_group_rmsnorm_mode(const float* o, int64_t ldo, const float* w, const void* z,
+                                  int64_t ldz, void* out, int64_t ldout, int T, int N, int group,
+                                  float eps, const float* aux, int64_t ld_aux, int H, float den_eps,
+                                  int gate_mode, int dtype, void* stream);
+/* Short causal convolution per channel with silu over the tokens of each batch entry:
+ * out[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] * x[t-j, c]), zeros before position 0.  state
+ * [slots, ld_state] fp32 holds each sequence's last taps-1 inputs ([taps-1, C], oldest first); it is
+ * read for the first tokens of a portion and replaced by the portion's last inputs.  out != x.       */
+int b200_causal_conv_silu(const void* x, int64_t ldx, const float* w, const float* bias, float* state,
+                          int64_t ld_state, const int64_t* slot, const int* tok_pos, const int* tok_b,
+                          const int* ext_start, const int* ext_len, void* out, int64_t ldo, int T,
+                          int bs, int C, int taps, int dtype, void* stream);
+/* Matrix-memory recurrence with a decay computed from the token, S [D, E] fp32 per head in
+ * state[slot[b]] ([H][D][E]; ignored when the portion starts at position 0).  q, k [T, G * D], v [T, H * E]
+ * in `dtype`; head h reads q/k head h / (H / G).
+ * mode 0 (delta rule): g = exp(-exp(a_log[h]) * softplus(decay_raw[t, h * D + r] + decay_bias[h * D + r]));
+ *   S <- diag(g) S; u = sigmoid(beta_raw[t, h]) * (v - S^T k); S += k u^T; o = S^T q, with q and k
+ *   divided by sqrt(sum(x^2) + unit_eps) and q multiplied by q_scale.
+ * mode 1 (state space): dt = softplus(decay_raw[t, h] + decay_bias[h]); S <- exp(-exp(a_log[h]) dt) S +
+ *   k (dt v)^T; o = S^T q + skip[h] v (skip NULL = 0); q, k as given.
+ * out fp32 [T, H * E].                                                                                */
+int64_t b200_delta_recurrence_state_width(int H, int D, int E);
+int b200_delta_recurrence(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                          int64_t ldv, const void* decay_raw, int64_t ld_decay, const float* decay_bias,
+                          const float* a_log, const void* beta_raw, int64_t ld_beta, const float* skip,
+                          float q_scale, float unit_eps, int mode, float* state, int64_t ld_state,
+                          const int64_t* slot, const int* tok_pos, const int* ext_start,
+                          const int* ext_len, float* out, int64_t ldo, int bs, int H, int G, int D, int E,
+                          int dtype, void* stream);
+/* Per token: q, k -> RMS norm per head over D with a weight [D] shared by the heads (NULL: no norm) ->
+ * rotation of the first rot_dims coordinates (pairing 0: 2i with 2i+1, 1: i with i + rot_dims / 2; angle
+ * tok_pos * (freq_hi + freq_lo)[i]); queries times head_scale[h] -> q_out fp32; keys -> pool row loc[t] at
+ * k_off; v rotated over all E coordinates with vfreq (NULL: as given) -> pool row at v_off.          */
+int b200_headnorm_rot_write(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                            int64_t ldv, const float* qw, const float* kw, float eps,
+                            const float* freq_hi, const float* freq_lo, int rot_dims,
+                            const float* vfreq_hi, const float* vfreq_lo, int pairing,
+                            const float* head_scale, const int* tok_pos, const int64_t* loc, void* pool,
+                            int64_t ld_pool, int k_off, int v_off, float* q_out, int64_t ldqo, int T,
+                            int H, int G, int D, int E, int dtype, void* stream);
+/* For every token whose position p completes a block ((p + 1) % P == 0): the fp32 mean of the pool rows
+ * of positions p-P+1 .. p -> pooled[req_to_token[p] / pdiv] (pdiv = P or 1).                         */
+int b200_pool_block_means(const void* pool, int64_t ld_pool, int width, float* pooled,
+                          int64_t ld_pooled, int P, int pdiv, const int* req_to_token, int64_t ld_r2t,
+                          const int64_t* req_idx, const int* tok_pos, const int* tok_b, int T, int dtype,
+                          void* stream);
+/* Softmax attention of every token over the window 0 <= p - j < window (0: all before) and, with
+ * `pooled`, the first max(0, p - window + 1) / P block rows of the summary buffer; fp32 queries (already
+ * scaled per head), one softmax over blocks and tokens; the output is rotated by -p over all E
+ * coordinates (vfreq NULL: not).                                                                     */
+int b200_pooled_window_attn(const float* q, int64_t ldq, const void* pool, int64_t ld_pool, int k_off,
+                            int v_off, const float* pooled, int64_t ld_pooled, int P, int pdiv,
+                            const int* req_to_token, int64_t ld_r2t, const int64_t* req_idx,
+                            const int* tok_pos, const int* tok_b, float scale, int window,
+                            const float* vfreq_hi, const float* vfreq_lo, int pairing, void* out,
+                            int64_t ldo, int T, int H, int G, int D, int E, const int* tok_list,
+                            int max_keys, int dtype, void* stream);
+/* Router with softmax scores over all experts: choice = s + correction (NULL: 0); experts in n_groups
+ * groups of neighbours, only the `keep` groups with the largest choice score take part; the `top`
+ * largest choice scores are chosen; weights = s of the chosen / (their sum + 1e-20).                 */
+int b200_moe_route_grouped(const void* h, int64_t ldh, const float* wr, const float* correction, int E,
+                           int W, int top, int n_groups, int keep, int* ids, float* wts, int T,
+                           int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

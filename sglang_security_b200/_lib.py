@@ -238,6 +238,37 @@ _SIGNATURES = {
                                         c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_void_p, c_int64, c_float, c_float, c_int, c_int,
                                         c_void_p]),
+    "b200_scaled_add_layernorm": (c_int, [c_void_p, c_int64, c_float, c_void_p, c_int64, c_void_p, c_int64,
+                                          c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_float,
+                                          c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_act_and_mul_clamped": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_float,
+                                         c_float, c_int, c_void_p]),
+    "b200_gated_group_rmsnorm_mode": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p,
+                                              c_int64, c_int, c_int, c_int, c_float, c_void_p, c_int64,
+                                              c_int, c_float, c_int, c_int, c_void_p]),
+    "b200_causal_conv_silu": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                      c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_delta_recurrence_state_width": (c_int64, [c_int, c_int, c_int]),
+    "b200_delta_recurrence": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                      c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float,
+                                      c_float, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                                      c_int, c_void_p]),
+    "b200_headnorm_rot_write": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                        c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                        c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_void_p]),
+    "b200_pool_block_means": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_int, c_void_p,
+                                      c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "b200_pooled_window_attn": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p,
+                                        c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p,
+                                        c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                        c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                        c_void_p]),
+    "b200_moe_route_grouped": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                       c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]),
 }
 
 

@@ -33,7 +33,7 @@ class ModelConfig:
         with open(os.path.join(model_path, "config.json")) as f:
             self.raw = json.load(f)
         self.architecture = architecture_of(self.raw)
-        from . import desirax, dozetar, kulesun  # noqa: F401  (register their configuration classes)
+        from . import desirax, dozetar, kisilix, kulesun  # noqa: F401  (register their configuration classes)
 
         if self.architecture not in _CONFIG_CLASSES:
             raise ValueError(f"no configuration class for architecture {self.architecture!r}; known: "

@@ -1,0 +1,341 @@
+// Recurrent mixers whose memory is a matrix S [D key rows, E value columns] per head, kept in fp32 and
+// carried from token to token, with a decay that is computed from the token (not a constant), and the
+// short causal convolution that feeds them.
+//
+//   causal_conv_silu  : y[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] * x[t-j, c]) over the tokens of a
+//                       sequence; x before position 0 is zero.  The inputs of a portion's first tokens
+//                       that lie before the portion come from the sequence's state row, which holds the
+//                       last taps-1 inputs ([taps-1, C] fp32, oldest first).
+//   conv_state_update : after the convolution has read it, the state row takes the last taps-1 inputs
+//                       of the portion (shifting what it held when the portion is shorter).
+//   delta_recurrence  : per (sequence, head), token by token
+//                         mode 0 (delta rule, a decay per key row):
+//                           g_r = exp(-exp(A_h) * softplus(raw[t, h, r] + bias[h, r]))
+//                           S <- diag(g) S ; u = beta (v - S^T k) ; S <- S + k u^T ; o = S^T q
+//                           with q, k divided by sqrt(sum(x^2) + unit_eps), q times q_scale, beta =
+//                           sigmoid(beta_raw[t, h])
+//                         mode 1 (state space, a scalar decay per head):
+//                           dt = softplus(raw[t, h] + bias[h]) ; a = exp(-exp(A_h) dt)
+//                           S <- a S + k (dt v)^T ; o = S^T q + skip_h v
+//                       A thread owns RPL rows of one value column in registers (LPC lanes share a column
+//                       and reduce by shuffles), so a token costs two passes over the thread's rows and
+//                       no shared-memory traffic for S.  Tokens are staged 16 at a time: keys, queries,
+//                       decays and step sizes of the chunk are prepared by all threads in parallel
+//                       (norms by one warp per token, exponentials element-wise), then the chunk is
+//                       walked in order.  Every sum is taken in an order that depends on neither the
+//                       chunking, the portion nor the CTA shape, so prefill, portions and single decoded
+//                       tokens give identical results.  State row layout: [H][D][E] fp32; a portion that
+//                       starts at position 0 ignores what the row holds.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kConvThreads = 256;
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+template <typename T>
+__global__ void __launch_bounds__(kConvThreads)
+causal_conv_silu_kernel(const T* __restrict__ x, int64_t ldx, const float* __restrict__ w,
+                        const float* __restrict__ bias, const float* __restrict__ state,
+                        int64_t ld_state, const int64_t* __restrict__ slot,
+                        const int* __restrict__ tok_pos, const int* __restrict__ tok_b,
+                        const int* __restrict__ ext_start, T* __restrict__ out, int64_t ldo, int C,
+                        int taps) {
+  const int t = blockIdx.x, c = blockIdx.y * kConvThreads + threadIdx.x;
+  if (c >= C) return;
+  const int b = tok_b[t], i = t - ext_start[b], p = tok_pos[t];
+  const float* st = state + slot[b] * ld_state;
+  float acc = bias ? bias[c] : 0.f;
+  for (int j = 0; j < taps && j <= p; ++j) {       // j tokens back; before position 0: zeros
+    const float xin = j <= i ? to_float<T>(x[static_cast<int64_t>(t - j) * ldx + c])
+                             : st[static_cast<int64_t>(taps - 1 - (j - i)) * C + c];
+    acc = fmaf(w[c * taps + taps - 1 - j], xin, acc);
+  }
+  out[t * ldo + c] = from_float<T>(acc / (1.0f + expf(-acc)));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kConvThreads)
+conv_state_update_kernel(const T* __restrict__ x, int64_t ldx, float* __restrict__ state,
+                         int64_t ld_state, const int64_t* __restrict__ slot,
+                         const int* __restrict__ tok_pos, const int* __restrict__ ext_start,
+                         const int* __restrict__ ext_len, int C, int taps) {
+  const int b = blockIdx.x, c = blockIdx.y * kConvThreads + threadIdx.x;
+  const int n = ext_len[b];
+  if (c >= C || n <= 0) return;
+  const int r0 = ext_start[b], p0 = tok_pos[r0];
+  float* st = state + slot[b] * ld_state;
+  for (int s = 0; s < taps - 1; ++s) {             // increasing s: what is read lies ahead of what is written
+    const int idx = n - (taps - 1) + s;            // the input to keep, relative to the portion's start
+    float v = 0.f;
+    if (idx >= 0) v = to_float<T>(x[static_cast<int64_t>(r0 + idx) * ldx + c]);
+    else if (p0 + idx >= 0) v = st[static_cast<int64_t>(s + n) * C + c];
+    st[static_cast<int64_t>(s) * C + c] = v;
+  }
+}
+
+constexpr int kDeltaChunk = 16;   // tokens staged at a time
+
+struct DeltaArgs {
+  const void *q, *k, *v;
+  int64_t ldq, ldk, ldv;
+  const void* decay_raw;
+  int64_t ld_decay;
+  const float* decay_bias;
+  const float* a_log;
+  const void* beta_raw;
+  int64_t ld_beta;
+  const float* skip;
+  float* state;
+  int64_t ld_state;
+  const int64_t* slot;
+  const int *tok_pos, *ext_start, *ext_len;
+  float* out;
+  int64_t ldo;
+  int H, G, D, E, lpc;
+  float q_scale, unit_eps;
+};
+
+template <typename T, int RPL, bool DELTA>
+__global__ void __launch_bounds__(128)
+delta_recurrence_kernel(const DeltaArgs a) {
+  extern __shared__ float dr_smem[];
+  const int b = blockIdx.x, h = blockIdx.y, LPC = a.lpc, Dp = RPL * LPC;
+  const int D = a.D, E = a.E, c = h / (a.H / a.G);
+  const int n = a.ext_len[b];
+  if (n <= 0) return;
+  const int row0 = a.ext_start[b], pos0 = a.tok_pos[row0];
+  float* ks = dr_smem;                         // [chunk][Dp]
+  float* qs = ks + kDeltaChunk * Dp;           // [chunk][Dp]
+  float* gs = qs + kDeltaChunk * Dp;           // [chunk][Dp] (delta) / [chunk] (scalar decay)
+  float* bs = gs + (DELTA ? kDeltaChunk * Dp : kDeltaChunk);   // [chunk] beta / dt
+  float* vs = bs + kDeltaChunk;                // [chunk][columns of this CTA]
+  const int tid = threadIdx.x, nt = blockDim.x, warp = tid >> 5, lane = tid & 31, nw = nt >> 5;
+  const int cols = nt / LPC, part = tid % LPC;
+  const int e = blockIdx.z * cols + tid / LPC;
+  const bool live = e < E;
+  const T* qg = static_cast<const T*>(a.q);
+  const T* kg = static_cast<const T*>(a.k);
+  const T* vg = static_cast<const T*>(a.v);
+  const T* dg = static_cast<const T*>(a.decay_raw);
+  const T* bg = static_cast<const T*>(a.beta_raw);
+  const float neg_a = -expf(a.a_log[h]);
+  const float skip = (!DELTA && a.skip) ? a.skip[h] : 0.f;
+  float* srow = a.state + a.slot[b] * a.ld_state + static_cast<int64_t>(h) * D * E;
+  float S[RPL];
+#pragma unroll
+  for (int i = 0; i < RPL; ++i) {
+    const int r = i * LPC + part;
+    S[i] = (pos0 > 0 && live && r < D) ? srow[static_cast<int64_t>(r) * E + e] : 0.f;
+  }
+  for (int t0 = 0; t0 < n; t0 += kDeltaChunk) {
+    const int m = min(kDeltaChunk, n - t0);
+    __syncthreads();                           // the previous chunk has been consumed
+    for (int idx = tid; idx < kDeltaChunk * Dp; idx += nt) {
+      const int tt = idx / Dp, r = idx - tt * Dp;
+      const bool ok = tt < m && r < D;
+      const int64_t row = row0 + t0 + tt;
+      ks[idx] = ok ? to_float<T>(kg[row * a.ldk + c * D + r]) : 0.f;
+      qs[idx] = ok ? to_float<T>(qg[row * a.ldq + c * D + r]) : 0.f;
+      if (DELTA)
+        gs[idx] = ok ? expf(neg_a * softplus_f(to_float<T>(dg[row * a.ld_decay + h * D + r]) +
+                                               a.decay_bias[h * D + r]))
+                     : 1.f;
+    }
+    for (int idx = tid; idx < kDeltaChunk * cols; idx += nt) {
+      const int tt = idx / cols, cl = idx - tt * cols, ee = blockIdx.z * cols + cl;
+      vs[idx] = (tt < m && ee < E) ? to_float<T>(vg[(row0 + t0 + tt) * a.ldv + h * E + ee]) : 0.f;
+    }
+    if (tid < kDeltaChunk) {
+      float bv = 0.f, gv = 1.f;
+      if (tid < m) {
+        const int64_t row = row0 + t0 + tid;
+        if (DELTA) {
+          bv = 1.0f / (1.0f + expf(-to_float<T>(bg[row * a.ld_beta + h])));
+        } else {
+          bv = softplus_f(to_float<T>(dg[row * a.ld_decay + h]) + a.decay_bias[h]);
+          gv = expf(neg_a * bv);
+        }
+      }
+      bs[tid] = bv;
+      if (!DELTA) gs[tid] = gv;
+    }
+    __syncthreads();
+    if (DELTA) {
+      // unit vectors: one warp per token, lanes stride over the rows, a fixed shuffle tree
+      for (int tt = warp; tt < m; tt += nw) {
+        float sk = 0.f, sq = 0.f;
+        for (int r = lane; r < D; r += 32) {
+          sk = fmaf(ks[tt * Dp + r], ks[tt * Dp + r], sk);
+          sq = fmaf(qs[tt * Dp + r], qs[tt * Dp + r], sq);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          sk += __shfl_xor_sync(0xffffffffu, sk, o);
+          sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        }
+        const float rk = 1.0f / sqrtf(sk + a.unit_eps), rq = a.q_scale / sqrtf(sq + a.unit_eps);
+        for (int r = lane; r < D; r += 32) {
+          ks[tt * Dp + r] *= rk;
+          qs[tt * Dp + r] *= rq;
+        }
+      }
+      __syncthreads();
+    }
+#pragma unroll 1
+    for (int tt = 0; tt < m; ++tt) {
+      {
+        const float vt = vs[tt * cols + tid / LPC];
+        const float* kt = ks + tt * Dp + part;
+        const float* qt = qs + tt * Dp + part;
+        float u;
+        if (DELTA) {
+          const float* gt = gs + tt * Dp + part;
+          float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+          for (int i = 0; i < RPL; i += 4) {
+            S[i] *= gt[i * LPC];
+            S[i + 1] *= gt[(i + 1) * LPC];
+            S[i + 2] *= gt[(i + 2) * LPC];
+            S[i + 3] *= gt[(i + 3) * LPC];
+            d0 = fmaf(S[i], kt[i * LPC], d0);
+            d1 = fmaf(S[i + 1], kt[(i + 1) * LPC], d1);
+            d2 = fmaf(S[i + 2], kt[(i + 2) * LPC], d2);
+            d3 = fmaf(S[i + 3], kt[(i + 3) * LPC], d3);
+          }
+          float dot = (d0 + d1) + (d2 + d3);
+          for (int o = 1; o < LPC; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          u = bs[tt] * (vt - dot);
+        } else {
+          const float g = gs[tt];
+#pragma unroll
+          for (int i = 0; i < RPL; ++i) S[i] *= g;
+          u = bs[tt] * vt;
+        }
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < RPL; i += 4) {
+          S[i] = fmaf(kt[i * LPC], u, S[i]);
+          S[i + 1] = fmaf(kt[(i + 1) * LPC], u, S[i + 1]);
+          S[i + 2] = fmaf(kt[(i + 2) * LPC], u, S[i + 2]);
+          S[i + 3] = fmaf(kt[(i + 3) * LPC], u, S[i + 3]);
+          o0 = fmaf(S[i], qt[i * LPC], o0);
+          o1 = fmaf(S[i + 1], qt[(i + 1) * LPC], o1);
+          o2 = fmaf(S[i + 2], qt[(i + 2) * LPC], o2);
+          o3 = fmaf(S[i + 3], qt[(i + 3) * LPC], o3);
+        }
+        float o = (o0 + o1) + (o2 + o3);
+        for (int off = 1; off < LPC; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+        if (live && part == 0) a.out[(row0 + t0 + tt) * a.ldo + h * E + e] = fmaf(skip, vt, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RPL; ++i) {
+    const int r = i * LPC + part;
+    if (live && r < D) srow[static_cast<int64_t>(r) * E + e] = S[i];
+  }
+}
+
+}  // namespace b200
+
+extern "C" int b200_causal_conv_silu(const void* x, int64_t ldx, const float* w, const float* bias,
+                                     float* state, int64_t ld_state, const int64_t* slot,
+                                     const int* tok_pos, const int* tok_b, const int* ext_start,
+                                     const int* ext_len, void* out, int64_t ldo, int T, int bs, int C,
+                                     int taps, int dtype, void* stream) {
+  using namespace b200;
+  if (T == 0) return 0;
+  B200_REQUIRE(x && w && state && slot && tok_pos && tok_b && ext_start && ext_len && out,
+               "b200_causal_conv_silu: null pointer");
+  B200_REQUIRE(T > 0 && bs > 0 && C > 0 && taps >= 1 && ld_state >= static_cast<int64_t>(taps - 1) * C,
+               "b200_causal_conv_silu: %d channels, %d taps, state row of %lld", C, taps,
+               static_cast<long long>(ld_state));
+  B200_REQUIRE(x != out, "b200_causal_conv_silu: the state update reads the inputs after the convolution");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("causal_conv_silu", st);
+  const int cb = ceil_div(C, kConvThreads);
+#define LAUNCH(TT)                                                                                   \
+  do {                                                                                               \
+    launch_kernel(causal_conv_silu_kernel<TT>, dim3(T, cb), dim3(kConvThreads), 0, st, 1, 0,        \
+                  static_cast<const TT*>(x), ldx, w, bias, state, ld_state, slot, tok_pos, tok_b,    \
+                  ext_start, static_cast<TT*>(out), ldo, C, taps);                                   \
+    B200_CHECK_LAUNCH("causal_conv_silu_kernel");                                                   \
+    if (taps > 1) {                                                                                  \
+      launch_kernel(conv_state_update_kernel<TT>, dim3(bs, cb), dim3(kConvThreads), 0, st, 1, 0,    \
+                    static_cast<const TT*>(x), ldx, state, ld_state, slot, tok_pos, ext_start,       \
+                    ext_len, C, taps);                                                               \
+      B200_CHECK_LAUNCH("conv_state_update_kernel");                                                \
+    }                                                                                                \
+  } while (0)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else if (dtype == B200_F32) LAUNCH(float);
+  else B200_REQUIRE(false, "b200_causal_conv_silu: dtype %d", dtype);
+#undef LAUNCH
+  return 0;
+}
+
+extern "C" int64_t b200_delta_recurrence_state_width(int H, int D, int E) {
+  return static_cast<int64_t>(H) * D * E;
+}
+
+extern "C" int b200_delta_recurrence(const void* q, int64_t ldq, const void* k, int64_t ldk,
+                                     const void* v, int64_t ldv, const void* decay_raw,
+                                     int64_t ld_decay, const float* decay_bias, const float* a_log,
+                                     const void* beta_raw, int64_t ld_beta, const float* skip,
+                                     float q_scale, float unit_eps, int mode, float* state,
+                                     int64_t ld_state, const int64_t* slot, const int* tok_pos,
+                                     const int* ext_start, const int* ext_len, float* out, int64_t ldo,
+                                     int bs, int H, int G, int D, int E, int dtype, void* stream) {
+  using namespace b200;
+  if (bs == 0) return 0;
+  B200_REQUIRE(q && k && v && decay_raw && decay_bias && a_log && state && slot && tok_pos && ext_start &&
+                   ext_len && out,
+               "b200_delta_recurrence: null pointer");
+  B200_REQUIRE(mode == 0 || mode == 1, "b200_delta_recurrence: mode %d", mode);
+  B200_REQUIRE(mode == 1 || beta_raw, "b200_delta_recurrence: the delta rule needs its write strengths");
+  B200_REQUIRE(bs > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && D <= 1024 && E > 0 && H <= 65535,
+               "b200_delta_recurrence: heads %d / %d, key rows %d, value columns %d", H, G, D, E);
+  B200_REQUIRE(ld_state >= static_cast<int64_t>(H) * D * E, "b200_delta_recurrence: state row too short");
+  const int rpl = D <= 16 ? 16 : 32;
+  int lpc = 1;
+  while (rpl * lpc < D) lpc <<= 1;
+  // one or two warps per CTA: enough CTAs to fill the machine when few sequences are in the step
+  int nt = 64;
+  if (static_cast<int64_t>(bs) * H * ceil_div(E * lpc, 64) < 2 * device_sm_count()) nt = 32;
+  const int cols = nt / lpc;
+  const dim3 grid(bs, H, ceil_div(E, cols));
+  const int Dp = rpl * lpc;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(kDeltaChunk) * Dp * (mode == 0 ? 3 : 2) +
+                                       2 * kDeltaChunk + static_cast<size_t>(kDeltaChunk) * cols);
+  B200_REQUIRE(smem <= 200 * 1024, "b200_delta_recurrence: key rows %d too many", D);
+  DeltaArgs a{q, k, v, ldq, ldk, ldv, decay_raw, ld_decay, decay_bias, a_log, beta_raw, ld_beta, skip,
+              state, ld_state, slot, tok_pos, ext_start, ext_len, out, ldo, H, G, D, E, lpc, q_scale,
+              unit_eps};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer(mode == 0 ? "delta_recurrence" : "ssm_recurrence", st);
+#define LAUNCH3(TT, R, DL)                                                                           \
+  do {                                                                                               \
+    if (smem > 48 * 1024)                                                                            \
+      B200_CUDA_OK(cudaFuncSetAttribute(delta_recurrence_kernel<TT, R, DL>,                          \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
+    launch_kernel(delta_recurrence_kernel<TT, R, DL>, grid, dim3(nt), smem, st, 1, 0, a);            \
+  } while (0)
+#define LAUNCH(TT)                                                                                   \
+  do {                                                                                               \
+    if (rpl == 16 && mode == 0) LAUNCH3(TT, 16, true);                                               \
+    else if (rpl == 16) LAUNCH3(TT, 16, false);                                                      \
+    else if (mode == 0) LAUNCH3(TT, 32, true);                                                       \
+    else LAUNCH3(TT, 32, false);                                                                     \
+  } while (0)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else if (dtype == B200_F32) LAUNCH(float);
+  else B200_REQUIRE(false, "b200_delta_recurrence: dtype %d", dtype);
+#undef LAUNCH
+#undef LAUNCH3
+  B200_CHECK_LAUNCH("delta_recurrence_kernel");
+  return 0;
+}

@@ -33,6 +33,7 @@
 //   gated_group_rmsnorm : out = o / sqrt(mean_group(o^2) + eps) * w * sigmoid(z), the mean taken over
 //                         consecutive groups of `group` coordinates (one head, or the whole row);
 //                         with the gated form's (n . q, m) per head, o is first divided as above.
+//                         Gate mode 1: o is multiplied by silu(z) BEFORE the norm instead.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -294,7 +295,7 @@ __global__ void __launch_bounds__(256)
 gated_group_rmsnorm_kernel(const float* __restrict__ o, int64_t ldo, const float* __restrict__ w,
                            const TZ* __restrict__ z, int64_t ldz, TO* __restrict__ out, int64_t ldout,
                            int N, int group, float eps, const float* __restrict__ aux, int64_t ld_aux,
-                           int H, float den_eps) {
+                           int H, float den_eps, int gate_mode) {
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* row = o + t * ldo;
   const int head_size = aux ? N / H : 1;
@@ -305,6 +306,10 @@ gated_group_rmsnorm_kernel(const float* __restrict__ o, int64_t ldo, const float
       if (aux) {
         const int hd = (g0 + d) / head_size;
         x /= fmaxf(fabsf(aux[t * ld_aux + hd]), expf(-aux[t * ld_aux + H + hd])) + den_eps;
+      }
+      if (gate_mode == 1) {                     // the gate silu(z) multiplies BEFORE the norm
+        const float zz = to_float<TZ>(z[t * ldz + g0 + d]);
+        x *= zz / (1.0f + expf(-zz));
       }
       ss = fmaf(x, x, ss);
     }
@@ -318,7 +323,10 @@ gated_group_rmsnorm_kernel(const float* __restrict__ o, int64_t ldo, const float
         y /= fmaxf(fabsf(aux[t * ld_aux + hd]), expf(-aux[t * ld_aux + H + hd])) + den_eps;
       }
       if (w) y *= w[g0 + d];
-      if (z) y *= 1.0f / (1.0f + expf(-to_float<TZ>(z[t * ldz + g0 + d])));
+      if (z) {
+        const float zz = to_float<TZ>(z[t * ldz + g0 + d]);
+        y *= gate_mode == 1 ? zz / (1.0f + expf(-zz)) : 1.0f / (1.0f + expf(-zz));
+      }
       out[t * ldout + g0 + d] = from_float<TO>(y);
     }
   }
@@ -429,12 +437,14 @@ extern "C" int b200_linear_recurrence(const void* q, int64_t ldq, const void* k,
 
 // aux (optional): fp32 [T, 2 H] = (n . q, m) of the gated recurrence; o is divided by
 // max(|n . q|, exp(-m)) + den_eps per (token, head) before the norm
-extern "C" int b200_gated_group_rmsnorm(const float* o, int64_t ldo, const float* w, const void* z,
-                                        int64_t ldz, void* out, int64_t ldout, int T, int N,
-                                        int group, float eps, const float* aux, int64_t ld_aux, int H,
-                                        float den_eps, int dtype, void* stream) {
+extern "C" int b200_gated_group_rmsnorm_mode(const float* o, int64_t ldo, const float* w, const void* z,
+                                             int64_t ldz, void* out, int64_t ldout, int T, int N,
+                                             int group, float eps, const float* aux, int64_t ld_aux,
+                                             int H, float den_eps, int gate_mode, int dtype,
+                                             void* stream) {
   using namespace b200;
   if (T == 0) return 0;
+  B200_REQUIRE(gate_mode == 0 || (gate_mode == 1 && z), "b200_gated_group_rmsnorm: gate mode %d", gate_mode);
   B200_REQUIRE(o && out && T > 0 && N > 0 && group > 0 && N % group == 0,
                "b200_gated_group_rmsnorm: %d coordinates in groups of %d", N, group);
   B200_REQUIRE(!aux || (H > 0 && N % H == 0), "b200_gated_group_rmsnorm: %d coordinates, %d heads", N, H);
@@ -443,7 +453,7 @@ extern "C" int b200_gated_group_rmsnorm(const float* o, int64_t ldo, const float
 #define LAUNCH(TT)                                                                                   \
   launch_kernel(gated_group_rmsnorm_kernel<TT, TT>, dim3(T), dim3(256), 0, st, 1, 0, o, ldo, w,      \
                 static_cast<const TT*>(z), ldz, static_cast<TT*>(out), ldout, N, group, eps, aux,    \
-                ld_aux, H, den_eps)
+                ld_aux, H, den_eps, gate_mode)
   if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
   else if (dtype == B200_F16) LAUNCH(__half);
   else if (dtype == B200_F32) LAUNCH(float);
@@ -451,4 +461,12 @@ extern "C" int b200_gated_group_rmsnorm(const float* o, int64_t ldo, const float
 #undef LAUNCH
   B200_CHECK_LAUNCH("gated_group_rmsnorm_kernel");
   return 0;
+}
+
+extern "C" int b200_gated_group_rmsnorm(const float* o, int64_t ldo, const float* w, const void* z,
+                                        int64_t ldz, void* out, int64_t ldout, int T, int N,
+                                        int group, float eps, const float* aux, int64_t ld_aux, int H,
+                                        float den_eps, int dtype, void* stream) {
+  return b200_gated_group_rmsnorm_mode(o, ldo, w, z, ldz, out, ldout, T, N, group, eps, aux, ld_aux, H,
+                                       den_eps, 0, dtype, stream);
 }

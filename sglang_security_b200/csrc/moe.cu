@@ -21,15 +21,13 @@ namespace b200 {
 
 constexpr int kMaxExpertsPerLane = 8;  // experts <= 256
 
+// Router logits of one token: the CTA's 8 warps share the experts' dot products (and the optional
+// shared-expert gate's); z_s[e] = w_e . h + b_e in fp32.
 template <typename T>
-__global__ void __launch_bounds__(256)
-moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__ wr,
-                 const float* __restrict__ br, int E, int W, int top, const float* __restrict__ wsg,
-                 int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int Tn,
-                 int score) {
-  // one CTA per token: its 8 warps share the experts' dot products (and the gate's), warp 0 ranks
-  __shared__ float z_s[32 * kMaxExpertsPerLane];
-  const int t = blockIdx.x;
+__device__ __forceinline__ void route_logits(const T* __restrict__ h, int64_t ldh,
+                                             const float* __restrict__ wr, const float* __restrict__ br,
+                                             int E, int W, const float* __restrict__ wsg,
+                                             float* __restrict__ gate, int t, float* z_s) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* row = h + t * ldh;
   const int jobs = E + ((wsg && gate) ? 1 : 0);
@@ -83,6 +81,19 @@ moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__
       else gate[t] = 1.0f / (1.0f + expf(-s));
     }
   }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__ wr,
+                 const float* __restrict__ br, int E, int W, int top, const float* __restrict__ wsg,
+                 int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int Tn,
+                 int score) {
+  // one CTA per token: its 8 warps share the experts' dot products (and the gate's), warp 0 ranks
+  __shared__ float z_s[32 * kMaxExpertsPerLane];
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  route_logits<T>(h, ldh, wr, br, E, W, wsg, gate, t, z_s);
   __syncthreads();
   if (warp != 0) return;
   float z[kMaxExpertsPerLane];
@@ -122,6 +133,111 @@ moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__
     if (lane == 0) ids[t * top + k] = bi;
   }
   if (lane < top) wts[t * top + lane] = score == 1 ? 1.0f / (1.0f + expf(-mine_z)) : mine / sum;
+}
+
+// Softmax scores over ALL experts, a choice among groups of neighbouring experts:
+//   s = softmax(z);  choice = s + correction;  a group's score is its largest choice score; only experts
+//   of the `keep` best groups can be chosen (the others count as minus infinity);  the `top` largest choice
+//   scores are taken (ties: lowest index);  weights = s of the chosen / (their sum + 1e-20).
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_route_grouped_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__ wr,
+                         const float* __restrict__ correction, int E, int W, int top, int n_groups,
+                         int keep, int* __restrict__ ids, float* __restrict__ wts) {
+  __shared__ float z_s[32 * kMaxExpertsPerLane];   // logits, then the scores s
+  __shared__ float c_s[32 * kMaxExpertsPerLane];   // choice scores
+  __shared__ float g_s[32 * kMaxExpertsPerLane];   // group scores
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  route_logits<T>(h, ldh, wr, nullptr, E, W, nullptr, nullptr, t, z_s);
+  __syncthreads();
+  if (warp != 0) return;
+  float zmax = -INFINITY;
+  for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z_s[e]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, o));
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float p = expf(z_s[e] - zmax);
+    z_s[e] = p;
+    sum += p;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  for (int e = lane; e < E; e += 32) {
+    z_s[e] /= sum;
+    c_s[e] = z_s[e] + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (n_groups > 1 && keep < n_groups) {
+    const int per = E / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      float gm = -INFINITY;
+      for (int i = 0; i < per; ++i) gm = fmaxf(gm, c_s[g * per + i]);
+      g_s[g] = gm;
+    }
+    __syncwarp();
+    // the `keep` best groups, one per round (ties: lowest index); a kept group's score becomes +inf
+    for (int k = 0; k < keep; ++k) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32) {
+        const float v = g_s[g];
+        if (v != INFINITY && (v > bv || (v == bv && g < bi))) {
+          bv = v;
+          bi = g;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+          bv = ov;
+          bi = oi;
+        }
+      }
+      if (lane == 0 && bi != 0x7fffffff) g_s[bi] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (g_s[e / per] != INFINITY) c_s[e] = -INFINITY;
+    __syncwarp();
+  }
+  float z[kMaxExpertsPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) z[i] = (lane + 32 * i < E) ? c_s[lane + 32 * i] : -INFINITY;
+  float wsum = 0.f, mine = 0.f;                 // lane k keeps the k-th chosen expert's score
+  for (int k = 0; k < top; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E && z[i] != -INFINITY && (z[i] > bv || (z[i] == bv && e < bi))) {
+        bv = z[i];
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (bi == 0x7fffffff) bi = 0;               // fewer allowed experts than `top` (rejected by the host)
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i)
+      if (bi == lane + 32 * i) z[i] = -INFINITY;
+    const float sc = z_s[bi];
+    wsum += sc;
+    if (lane == k) mine = sc;
+    if (lane == 0) ids[t * top + k] = bi;
+  }
+  if (lane < top) wts[t * top + lane] = mine / (wsum + 1e-20f);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -504,4 +620,29 @@ extern "C" int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, 
                                      void* stream) {
   return b200_moe_grouped_gemm_mode(a, lda, w, ldw, w_expert_stride, offsets, sorted_rows, E, top, rows,
                                     Nout, K, out, ldo, gated ? 1 : 0, act, nullptr, dtype, stream);
+}
+
+extern "C" int b200_moe_route_grouped(const void* h, int64_t ldh, const float* wr, const float* correction,
+                                      int E, int W, int top, int n_groups, int keep, int* ids, float* wts,
+                                      int T, int dtype, void* stream) {
+  using namespace b200;
+  if (T == 0) return 0;
+  B200_REQUIRE(h && wr && ids && wts, "b200_moe_route_grouped: null pointer");
+  B200_REQUIRE(E > 0 && E <= 32 * kMaxExpertsPerLane && top > 0 && top <= E && top <= 32 && W > 0,
+               "b200_moe_route_grouped: experts %d (max %d), top %d", E, 32 * kMaxExpertsPerLane, top);
+  B200_REQUIRE(n_groups >= 1 && E % n_groups == 0 && keep >= 1 && keep <= n_groups &&
+                   keep * (E / n_groups) >= top,
+               "b200_moe_route_grouped: %d experts in %d groups, %d kept, top %d", E, n_groups, keep, top);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("moe_route", st);
+#define LAUNCH(TT)                                                                                   \
+  launch_kernel(moe_route_grouped_kernel<TT>, dim3(T), dim3(256), 0, st, 1, 0,                      \
+                static_cast<const TT*>(h), ldh, wr, correction, E, W, top, n_groups, keep, ids, wts)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else if (dtype == B200_F32) LAUNCH(float);
+  else B200_REQUIRE(false, "b200_moe_route_grouped: dtype %d", dtype);
+#undef LAUNCH
+  B200_CHECK_LAUNCH("moe_route_grouped_kernel");
+  return 0;
 }

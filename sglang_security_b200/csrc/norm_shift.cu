@@ -14,6 +14,14 @@
 //                          the NEXT sublayer's pre-norm instead, x / sqrt(mean(x^2) + eps) * w_next (designs
 //                          with a norm on both sides of every sublayer: one launch per sublayer boundary)
 //   softcap_rows         : out = cap * tanh(z / cap) in fp32
+//   scaled_add_layernorm : for designs whose norm sits AFTER the residual sum: y = alpha * x + a + b +
+//                          sum_k wts[t, k] * rows[t * top + k] (terms optional) in fp32, then
+//                          x = (y - mean) / sqrt(var + eps) * w + bias (two passes: the variance is the
+//                          mean of the squared deviations); optionally the copy of the new x in the
+//                          model dtype.  With `in_place` = 0 x is left alone and only the copy is
+//                          written (a model's final layer norm).
+//   act_and_mul_clamped  : out = g * sigmoid(slope * g) * (u + 1), g = min(z[:, :d], limit),
+//                          u = clamp(z[:, d:], -limit, limit)
 #include "common.cuh"
 
 namespace b200 {
@@ -182,6 +190,54 @@ softcap_rows_kernel(const T* __restrict__ z, int64_t ldz, float* __restrict__ ou
   }
 }
 
+template <typename TA, typename TO>
+__global__ void __launch_bounds__(kRowThreads)
+scaled_add_layernorm_kernel(float* __restrict__ x, int64_t ldx, float alpha, const TA* __restrict__ a,
+                            int64_t lda, const TA* __restrict__ b, int64_t ldb,
+                            const TA* __restrict__ rows, int64_t ld_rows,
+                            const float* __restrict__ wts, int top, const float* __restrict__ w,
+                            const float* __restrict__ bias, float eps, TO* __restrict__ out_h,
+                            int64_t ldh, int W, int in_place) {
+  extern __shared__ float ln_row[];          // [W] the summed row
+  __shared__ float red[kRowThreads / 32];
+  const int t = blockIdx.x;
+  float s = 0.f;
+  for (int d = threadIdx.x; d < W; d += kRowThreads) {
+    float v = alpha * x[t * ldx + d];
+    if (a) v += to_float<TA>(a[t * lda + d]);
+    if (rows)
+      for (int k = 0; k < top; ++k)
+        v = fmaf(wts ? wts[t * top + k] : 1.f, to_float<TA>(rows[(static_cast<int64_t>(t) * top + k) * ld_rows + d]), v);
+    if (b) v += to_float<TA>(b[t * ldb + d]);
+    ln_row[d] = v;
+    s += v;
+  }
+  const float mean = block_sum(s, red) / static_cast<float>(W);
+  float q = 0.f;
+  for (int d = threadIdx.x; d < W; d += kRowThreads) {
+    const float c = ln_row[d] - mean;
+    q = fmaf(c, c, q);
+  }
+  const float r = 1.0f / sqrtf(block_sum(q, red) / static_cast<float>(W) + eps);
+  for (int d = threadIdx.x; d < W; d += kRowThreads) {
+    const float y = fmaf((ln_row[d] - mean) * r, w ? w[d] : 1.f, bias ? bias[d] : 0.f);
+    if (in_place) x[t * ldx + d] = y;
+    if (out_h) out_h[t * ldh + d] = from_float<TO>(y);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+act_and_mul_clamped_kernel(const T* __restrict__ z, int64_t ldz, T* __restrict__ out, int64_t ldo, int D,
+                           float limit, float slope) {
+  const int t = blockIdx.x;
+  for (int d = threadIdx.x; d < D; d += kRowThreads) {
+    const float g = fminf(to_float<T>(z[t * ldz + d]), limit);
+    const float u = fminf(fmaxf(to_float<T>(z[t * ldz + D + d]), -limit), limit);
+    out[t * ldo + d] = from_float<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+  }
+}
+
 }  // namespace b200
 
 extern "C" int b200_scalar_rmsnorm_shift(const float* x, int64_t ldx, const float* gain,
@@ -304,5 +360,60 @@ extern "C" int b200_softcap_rows(const void* z, int64_t ldz, float* out, int64_t
   else B200_REQUIRE(false, "b200_softcap_rows: dtype %d", dtype);
 #undef LAUNCH
   B200_CHECK_LAUNCH("softcap_rows_kernel");
+  return 0;
+}
+
+extern "C" int b200_scaled_add_layernorm(float* x, int64_t ldx, float alpha, const void* a, int64_t lda,
+                                         const void* b, int64_t ldb, const void* rows, int64_t ld_rows,
+                                         const float* wts, int top, const float* w, const float* bias,
+                                         float eps, void* out_h, int64_t ldh, int in_place, int T, int W,
+                                         int dtype, int out_dtype, void* stream) {
+  using namespace b200;
+  if (T == 0) return 0;
+  B200_REQUIRE(x && T > 0 && W > 0 && (in_place || out_h), "b200_scaled_add_layernorm: bad arguments");
+  B200_REQUIRE(!rows || top > 0, "b200_scaled_add_layernorm: rows without a count per token");
+  B200_REQUIRE(out_dtype == dtype || out_dtype == B200_F32 || !out_h,
+               "b200_scaled_add_layernorm: the copy has the terms' dtype or fp32");
+  const size_t smem = sizeof(float) * static_cast<size_t>(W);
+  B200_REQUIRE(smem <= 200 * 1024, "b200_scaled_add_layernorm: width %d too large", W);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("scaled_add_layernorm", st);
+#define LAUNCH(TA, TO)                                                                               \
+  do {                                                                                               \
+    if (smem > 48 * 1024)                                                                            \
+      B200_CUDA_OK(cudaFuncSetAttribute(scaled_add_layernorm_kernel<TA, TO>,                         \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
+    launch_kernel(scaled_add_layernorm_kernel<TA, TO>, dim3(T), dim3(kRowThreads), smem, st, 1, 0, x, \
+                  ldx, alpha, static_cast<const TA*>(a), lda, static_cast<const TA*>(b), ldb,        \
+                  static_cast<const TA*>(rows), ld_rows, wts, top, w, bias, eps,                     \
+                  static_cast<TO*>(out_h), ldh, W, in_place);                                        \
+  } while (0)
+  if (dtype == B200_BF16 && out_dtype == B200_F32) LAUNCH(__nv_bfloat16, float);
+  else if (dtype == B200_F16 && out_dtype == B200_F32) LAUNCH(__half, float);
+  else if (dtype == B200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half, __half);
+  else if (dtype == B200_F32) LAUNCH(float, float);
+  else B200_REQUIRE(false, "b200_scaled_add_layernorm: dtype %d", dtype);
+#undef LAUNCH
+  B200_CHECK_LAUNCH("scaled_add_layernorm_kernel");
+  return 0;
+}
+
+extern "C" int b200_act_and_mul_clamped(const void* z, int64_t ldz, void* out, int64_t ldo, int T, int D,
+                                        float limit, float slope, int dtype, void* stream) {
+  using namespace b200;
+  if (T == 0) return 0;
+  B200_REQUIRE(z && out && T > 0 && D > 0 && limit > 0.f, "b200_act_and_mul_clamped: bad arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("act_and_mul_clamped", st);
+#define LAUNCH(TT)                                                                                   \
+  launch_kernel(act_and_mul_clamped_kernel<TT>, dim3(T), dim3(kRowThreads), 0, st, 1, 0,            \
+                static_cast<const TT*>(z), ldz, static_cast<TT*>(out), ldo, D, limit, slope)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else if (dtype == B200_F32) LAUNCH(float);
+  else B200_REQUIRE(false, "b200_act_and_mul_clamped: dtype %d", dtype);
+#undef LAUNCH
+  B200_CHECK_LAUNCH("act_and_mul_clamped_kernel");
   return 0;
 }

@@ -78,3 +78,24 @@ class GatedActAndMul(nn.Module):
                                           _lib.current_stream())
         _lib.check(rc, "b200_act_and_mul")
         return out.view(x.shape[:-1] + (d,))
+
+
+class ClampedGluAndMul(nn.Module):
+    """g * sigmoid(slope * g) * (u + 1) with g = min(x[..., :d], limit), u = clamp(x[..., d:], -limit, limit),
+    for bf16 / f16 / fp32 rows.  One launch of b200_act_and_mul_clamped."""
+
+    def __init__(self, limit: float, slope: float = 1.702):
+        super().__init__()
+        if not limit > 0:
+            raise ValueError(f"the clamp limit must be positive, not {limit}")
+        self.limit, self.slope = float(limit), float(slope)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        d = x.shape[-1] // 2
+        x2 = _rows(x)
+        out = torch.empty((x2.shape[0], d), dtype=x.dtype, device=x.device)
+        rc = _lib.load().b200_act_and_mul_clamped(x2.data_ptr(), x2.stride(0), out.data_ptr(), out.stride(0),
+                                                  x2.shape[0], d, self.limit, self.slope,
+                                                  _lib.dtype_code(x2.dtype), _lib.current_stream())
+        _lib.check(rc, "b200_act_and_mul_clamped")
+        return out.view(x.shape[:-1] + (d,))

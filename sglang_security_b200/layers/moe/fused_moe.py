@@ -3,6 +3,10 @@
     TopKRouter   : z = W_r h + b in fp32; the `top` largest logits; weights = softmax over the chosen
                    logits only, or (score="sigmoid") the sigmoid of each chosen logit, not
                    renormalised.  Optionally the scalar gate sigmoid(w_sg . h) of a shared expert.
+    GroupedSoftmaxRouter : z = W_r h in fp32; scores s = softmax(z) over ALL experts; the choice is made
+                   on s + correction, among the experts of the `keep` groups (of `groups` equal groups
+                   of neighbours) whose best choice score is largest; weights = the chosen experts' s,
+                   divided by their sum (+ 1e-20).
     FusedExperts : all experts' gated feed-forwards W_down (act(W_gate h) * (W_up h)) as two grouped
                    GEMMs over the (token, choice) rows sorted by expert; nothing is read back to the
                    host, so the step stays capturable.  Returns one row per (token, choice); the
@@ -52,6 +56,32 @@ class TopKRouter(nn.Module):
             self.score, _lib.dtype_code(h.dtype), _lib.current_stream())
         _lib.check(rc, "b200_moe_route")
         return ids, wts, gate
+
+
+class GroupedSoftmaxRouter(nn.Module):
+    def __init__(self, width: int, experts: int, top: int, groups: int = 1, keep: int = 1,
+                 correction: bool = True):
+        super().__init__()
+        if experts % groups or not 0 < keep <= groups or keep * (experts // groups) < top:
+            raise ValueError(f"{experts} experts in {groups} groups, {keep} kept, top {top}")
+        self.experts, self.top, self.groups, self.keep = experts, top, groups, keep
+        self.weight = nn.Parameter(torch.zeros(experts, width, dtype=torch.float32), requires_grad=False)
+        self.correction = (nn.Parameter(torch.zeros(experts, dtype=torch.float32), requires_grad=False)
+                           if correction else None)
+
+    def forward(self, h: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """h [T, width] (fp32 or the model dtype) -> (ids int32 [T, top], weights fp32 [T, top])."""
+        if not h.is_cuda:
+            raise _lib.B200Error("GroupedSoftmaxRouter: tensor must live on a CUDA device (no CPU path)")
+        t, w = h.shape
+        ids = torch.empty((t, self.top), dtype=torch.int32, device=h.device)
+        wts = torch.empty((t, self.top), dtype=torch.float32, device=h.device)
+        rc = _lib.load().b200_moe_route_grouped(
+            h.data_ptr(), h.stride(0), self.weight.data_ptr(), _lib.ptr(self.correction), self.experts, w,
+            self.top, self.groups, self.keep, ids.data_ptr(), wts.data_ptr(), t, _lib.dtype_code(h.dtype),
+            _lib.current_stream())
+        _lib.check(rc, "b200_moe_route_grouped")
+        return ids, wts
 
 
 class FusedExperts(nn.Module):

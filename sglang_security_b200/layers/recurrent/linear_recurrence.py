@@ -66,19 +66,22 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: 
 
 def gated_group_rmsnorm(o: torch.Tensor, weight: Optional[torch.Tensor], z: Optional[torch.Tensor],
                         group: int, eps: float, out_dtype: torch.dtype, aux: Optional[torch.Tensor] = None,
-                        heads: int = 0, den_eps: float = 1e-6) -> torch.Tensor:
+                        heads: int = 0, den_eps: float = 1e-6, gate: str = "sigmoid") -> torch.Tensor:
     """o fp32 [T, N] -> o / rms over groups of `group` coordinates * weight * sigmoid(z), in out_dtype.
+    gate="silu_before": o is multiplied by silu(z) BEFORE the norm instead (the norm sees the gated values).
     With `aux` (the gated recurrence's (n . q, m), fp32 [T, 2 * heads]) each head of o is first divided
     by max(|n . q|, exp(-m)) + den_eps."""
     T, N = o.shape
     if z is not None and (z.dtype != out_dtype or z.stride(-1) != 1):
         raise _lib.B200Error("gated_group_rmsnorm: the gate must have the output dtype and contiguous rows")
     out = torch.empty((T, N), dtype=out_dtype, device=o.device)
-    rc = _lib.load().b200_gated_group_rmsnorm(
+    if gate not in ("sigmoid", "silu_before"):
+        raise ValueError(f"unknown gate form {gate!r}")
+    rc = _lib.load().b200_gated_group_rmsnorm_mode(
         o.data_ptr(), o.stride(0), _lib.ptr(weight), _lib.ptr(z), z.stride(0) if z is not None else 0,
         out.data_ptr(), out.stride(0), T, N, int(group), float(eps), _lib.ptr(aux),
-        aux.stride(0) if aux is not None else 0, int(heads), float(den_eps), _lib.dtype_code(out_dtype),
-        _lib.current_stream())
+        aux.stride(0) if aux is not None else 0, int(heads), float(den_eps),
+        1 if gate == "silu_before" else 0, _lib.dtype_code(out_dtype), _lib.current_stream())
     _lib.check(rc, "b200_gated_group_rmsnorm")
     return out
 

@@ -33,13 +33,18 @@ class ModelRunner:
         pages = (max_total_tokens + page_size - 1) // page_size
         self.max_total_tokens = pages * page_size
         self.context_length = context_length or self.max_total_tokens
+        # a model with a table of learned positions cannot run past it
+        limit = getattr(self.model, "max_positions", None)
+        if limit:
+            self.context_length = min(self.context_length, int(limit))
         self.max_running_requests = max_running_requests
         spec = self.model.cache_spec()
         if spec.kind not in ("latent", "rows"):
             raise ValueError(f"cache kind {spec.kind!r} is not served by this runner")
         self.req_to_token_pool = ReqToTokenPool(max_running_requests, self.context_length, device)
         self.token_to_kv_pool = LatentTokenToKVPool(self.max_total_tokens, page_size, dtype,
-                                                    spec.row_dims, spec.source_of, device)
+                                                    spec.row_dims, spec.source_of, device,
+                                                    block_summaries=spec.block_summaries)
         self.allocator = PagedTokenToKVPoolAllocator(self.max_total_tokens, page_size, dtype, device,
                                                      kvcache=self.token_to_kv_pool)
         self.state_pool = SeqStatePool(max_running_requests, spec.state_widths, device)

@@ -22,6 +22,7 @@ class CacheSpec:
                                                                # without an entry cache nothing per token)
     source_of: Dict[int, int] = field(default_factory=dict)    # layer -> layer whose rows it reads
     state_widths: Dict[int, int] = field(default_factory=dict)  # layer -> fp32 carry width per sequence
+    block_summaries: Dict[int, int] = field(default_factory=dict)  # layer -> tokens per summarised block
 
 
 def register_model(architecture: str):
@@ -32,7 +33,7 @@ def register_model(architecture: str):
 
 
 def resolve_model_cls(architecture: str):
-    from . import desirax, dozetar, kulesun  # noqa: F401  (register themselves)
+    from . import desirax, dozetar, kisilix, kulesun  # noqa: F401  (register themselves)
 
     if architecture not in _MODELS:
         raise ValueError(f"architecture {architecture!r} is not supported; known: {sorted(_MODELS)}")
@@ -40,6 +41,6 @@ def resolve_model_cls(architecture: str):
 
 
 def supported_architectures():
-    from . import desirax, dozetar, kulesun  # noqa: F401
+    from . import desirax, dozetar, kisilix, kulesun  # noqa: F401
 
     return sorted(_MODELS)
