@@ -49,6 +49,23 @@ def unit(x, eps=1e-6):
 
 
 # ---- gated delta rule with a decay per key channel ------------------------------------------------
+def delta_rule_scan(q, k, v, g, beta):
+    """q, k [T, G, D], v [T, H, E], g [T, H, D], beta [T, H] -> [T, H, E]; the memory starts at zero and the
+    read-out sees the current token's write."""
+    T, H, E = v.shape
+    G, D = q.shape[1], q.shape[2]
+    out = torch.zeros(T, H, E, dtype=F64)
+    for hh in range(H):
+        c = hh // (H // G)
+        S = torch.zeros(D, E, dtype=F64)
+        for t in range(T):
+            S = g[t, hh].view(D, 1) * S
+            u = beta[t, hh] * (v[t, hh] - S.T @ k[t, c])
+            S = S + torch.outer(k[t, c], u)
+            out[t, hh] = S.T @ q[t, c]
+    return out
+
+
 def channel_delta(h, W, p, m, eps):
     T = h.shape[0]
     H, G, D, E = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"]
@@ -61,20 +78,26 @@ def channel_delta(h, W, p, m, eps):
     low = (h @ W[p + "a1"].T) @ W[p + "a2"].T + W[p + "dt_bias"]              # [T, H * D]
     g = torch.exp(-torch.exp(W[p + "A_log"]).view(1, H, 1) * softplus(low).view(T, H, D))
     gate = torch.sigmoid((h @ W[p + "g1"].T) @ W[p + "g2"].T).view(T, H, E)
-    out = torch.zeros(T, H, E, dtype=F64)
-    for hh in range(H):
-        c = hh // (H // G)
-        S = torch.zeros(D, E, dtype=F64)
-        for t in range(T):
-            S = g[t, hh].view(D, 1) * S
-            u = beta[t, hh] * (v[t, hh] - S.T @ k[t, c])
-            S = S + torch.outer(k[t, c], u)
-            out[t, hh] = S.T @ q[t, c]
+    out = delta_rule_scan(q, k, v, g, beta)
     out = rms_div(out, eps) * W[p + "norm"] * gate
     return out.reshape(T, H * E) @ W[p + "o"].T
 
 
 # ---- state-space recurrence with a scalar decay per head -----------------------------------------
+def state_space_scan(C, B, x, a, dt, skip):
+    """C, B [T, G, N], x [T, H, E], a, dt [T, H], skip [H] -> [T, H, E]."""
+    T, H, E = x.shape
+    G, N = B.shape[1], B.shape[2]
+    out = torch.zeros(T, H, E, dtype=F64)
+    for hh in range(H):
+        c = hh // (H // G)
+        S = torch.zeros(N, E, dtype=F64)
+        for t in range(T):
+            S = a[t, hh] * S + dt[t, hh] * torch.outer(B[t, c], x[t, hh])
+            out[t, hh] = S.T @ C[t, c] + skip[hh] * x[t, hh]
+    return out
+
+
 def mamba2(h, W, p, m, eps):
     T = h.shape[0]
     H, E, N, G = m["heads"], m["vdim"], m["state"], m.get("groups", 1)
@@ -88,13 +111,7 @@ def mamba2(h, W, p, m, eps):
     C = xbc[:, inner + G * N:].view(T, G, N)
     dt = softplus(dt + W[p + "dt_bias"])                                       # [T, H]
     a = torch.exp(-torch.exp(W[p + "A_log"]) * dt)
-    out = torch.zeros(T, H, E, dtype=F64)
-    for hh in range(H):
-        c = hh // (H // G)
-        S = torch.zeros(N, E, dtype=F64)
-        for t in range(T):
-            S = a[t, hh] * S + dt[t, hh] * torch.outer(B[t, c], x[t, hh])
-            out[t, hh] = S.T @ C[t, c] + W[p + "D"][hh] * x[t, hh]
+    out = state_space_scan(C, B, x, a, dt, W[p + "D"])
     o = out.reshape(T, inner) * silu(z)
     o = rms_div(o.view(T, parts, inner // parts), eps).reshape(T, inner) * W[p + "norm"]
     return o @ W[p + "o"].T
@@ -120,6 +137,23 @@ def visible(i, size, pool):
     return toks, blocks
 
 
+def attend(q, k, v, size, pool, head_scale):
+    """q [T, H, D], k [T, G, D], v [T, G, E] of one sequence from position 0, head_scale [H] -> [T, H, E]:
+    one softmax over the visible tokens and the means of the visible blocks."""
+    T, H, _ = q.shape
+    G, E = k.shape[1], v.shape[2]
+    out = torch.zeros(T, H, E, dtype=F64)
+    for i in range(T):
+        toks, blocks = visible(i, size, pool)
+        for hh in range(H):
+            c = hh // (H // G)
+            keys = [k[b * pool:(b + 1) * pool, c].mean(0) for b in blocks] + [k[j, c] for j in toks]
+            vals = [v[b * pool:(b + 1) * pool, c].mean(0) for b in blocks] + [v[j, c] for j in toks]
+            sc = torch.stack(keys) @ q[i, hh] * head_scale[hh]
+            out[i, hh] = torch.softmax(sc, 0) @ torch.stack(vals)
+    return out
+
+
 def attention(h, W, p, m, eps, pos0=0):
     T = h.shape[0]
     H, G, D, E = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"]
@@ -135,15 +169,7 @@ def attention(h, W, p, m, eps, pos0=0):
         q = rotate_halves(q, pos, rot["base"], rot["dims"])
         k = rotate_halves(k, pos, rot["base"], rot["dims"])
         v = rotate_halves(v, pos, rot["base"], E)
-    out = torch.zeros(T, H, E, dtype=F64)
-    for i in range(T):
-        toks, blocks = visible(i, size, pool)
-        for hh in range(H):
-            c = hh // (H // G)
-            keys = [k[b * pool:(b + 1) * pool, c].mean(0) for b in blocks] + [k[j, c] for j in toks]
-            vals = [v[b * pool:(b + 1) * pool, c].mean(0) for b in blocks] + [v[j, c] for j in toks]
-            sc = torch.stack(keys) @ q[i, hh] * m["scale"] * W[p + "temp"][hh]
-            out[i, hh] = torch.softmax(sc, 0) @ torch.stack(vals)
+    out = attend(q, k, v, size, pool, m["scale"] * W[p + "temp"])
     if rot:
         out = rotate_halves(out, -pos, rot["base"], E)
     return out.reshape(T, H * E) @ W[p + "o"].T
