@@ -549,10 +549,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--arch-compare", default=None, metavar="SIZES",
                     help="instead of the headline workload: prefill / decode throughput of the Desirax, "
-                         "Dozetar and Kulesun designs beside the Llama-family stack at equal size ('all' or "
-                         "comma-separated names of model_executor/arch_bench.py SIZES / DOZETAR_SIZES / "
-                         "KULESUN_SIZES, e.g. dz-w1024,ku-w1024; a Kulesun size also runs the Desirax stack at "
-                         "equal size); one JSON line per model and size")
+                         "Dozetar, Kulesun and Kisilix designs beside the Llama-family stack at equal size ('all' "
+                         "or comma-separated names of model_executor/arch_bench.py SIZES / DOZETAR_SIZES / "
+                         "KULESUN_SIZES / KISILIX_SIZES, e.g. dz-w1024,ku-w1024,ki-w1024; a Kulesun size also runs "
+                         "the Desirax stack, a Kisilix size the Dozetar stack, at equal size); one JSON line per "
+                         "model and size")
     args = ap.parse_args()
     if args.arch_compare:
         from sglang_security_b200 import build as _build

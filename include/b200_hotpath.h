@@ -764,26 +764,31 @@ int b200_causal_conv_silu(const void* x, int64_t ldx, const float* w, const floa
  *   divided by sqrt(sum(x^2) + unit_eps) and q multiplied by q_scale.
  * mode 1 (state space): dt = softplus(decay_raw[t, h] + decay_bias[h]); S <- exp(-exp(a_log[h]) dt) S +
  *   k (dt v)^T; o = S^T q + skip[h] v (skip NULL = 0); q, k as given.
- * out fp32 [T, H * E].                                                                                */
+ * out fp32 [T, H * E].
+ * work: fp32 workspace of T * b200_delta_recurrence_work_width floats, 16-byte aligned (T = all tokens).
+ */
 int64_t b200_delta_recurrence_state_width(int H, int D, int E);
+int64_t b200_delta_recurrence_work_width(int H, int G, int D, int mode);
 int b200_delta_recurrence(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
                           int64_t ldv, const void* decay_raw, int64_t ld_decay, const float* decay_bias,
                           const float* a_log, const void* beta_raw, int64_t ld_beta, const float* skip,
                           float q_scale, float unit_eps, int mode, float* state, int64_t ld_state,
                           const int64_t* slot, const int* tok_pos, const int* ext_start,
-                          const int* ext_len, float* out, int64_t ldo, int bs, int H, int G, int D, int E,
-                          int dtype, void* stream);
+                          const int* ext_len, float* out, int64_t ldo, float* work, int T, int bs, int H,
+                          int G, int D, int E, int dtype, void* stream);
 /* Per token: q, k -> RMS norm per head over D with a weight [D] shared by the heads (NULL: no norm) ->
  * rotation of the first rot_dims coordinates (pairing 0: 2i with 2i+1, 1: i with i + rot_dims / 2; angle
- * tok_pos * (freq_hi + freq_lo)[i]); queries times head_scale[h] -> q_out fp32; keys -> pool row loc[t] at
- * k_off; v rotated over all E coordinates with vfreq (NULL: as given) -> pool row at v_off.          */
+ * tok_pos * (freq_hi + freq_lo)[i]); queries times head_scale[h] -> q_out fp32 (and q_out16 in `dtype`, if
+ * given, for the tensor-core kernel); keys -> pool row loc[t] at k_off; v rotated over all E coordinates
+ * with vfreq (NULL: as given) -> pool row at v_off.                                                  */
 int b200_headnorm_rot_write(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
                             int64_t ldv, const float* qw, const float* kw, float eps,
                             const float* freq_hi, const float* freq_lo, int rot_dims,
                             const float* vfreq_hi, const float* vfreq_lo, int pairing,
                             const float* head_scale, const int* tok_pos, const int64_t* loc, void* pool,
-                            int64_t ld_pool, int k_off, int v_off, float* q_out, int64_t ldqo, int T,
-                            int H, int G, int D, int E, int dtype, void* stream);
+                            int64_t ld_pool, int k_off, int v_off, float* q_out, int64_t ldqo,
+                            void* q_out16, int64_t ldqo16, int T, int H, int G, int D, int E, int dtype,
+                            void* stream);
 /* For every token whose position p completes a block ((p + 1) % P == 0): the fp32 mean of the pool rows
  * of positions p-P+1 .. p -> pooled[req_to_token[p] / pdiv] (pdiv = P or 1).                         */
 int b200_pool_block_means(const void* pool, int64_t ld_pool, int width, float* pooled,
@@ -801,6 +806,32 @@ int b200_pooled_window_attn(const float* q, int64_t ldq, const void* pool, int64
                             const float* vfreq_hi, const float* vfreq_lo, int pairing, void* out,
                             int64_t ldo, int T, int H, int G, int D, int E, const int* tok_list,
                             int max_keys, int dtype, void* stream);
+/* The block part of b200_pooled_window_attn alone: part_out fp32 [T, H * E] = softmax over the visible
+ * blocks' keys applied to their values (0 where no block is in sight), part_lse [T, H] = log2 of the
+ * softmax denominator (scaled scores as exponents of e; -inf where none).                            */
+int b200_pooled_blocks_attn_part(const float* q, int64_t ldq, const void* pool, int64_t ld_pool, int k_off,
+                                 int v_off, const float* pooled, int64_t ld_pooled, int P, int pdiv,
+                                 const int* req_to_token, int64_t ld_r2t, const int64_t* req_idx,
+                                 const int* tok_pos, const int* tok_b, float scale, int window,
+                                 float* part_out, int64_t ld_part, float* part_lse, int64_t ld_lse, int T,
+                                 int H, int G, int D, int E, const int* tok_list, int max_keys, int dtype,
+                                 void* stream);
+/* Rows tok_list[0..T) of out [., H * E] (normalised sums over one key set, with the log2 of their
+ * denominators lse1) are merged with a second normalised part (fp32, lse2; NULL: nothing to merge) as one
+ * softmax over both key sets, then rotated by -tok_pos over all E coordinates (vfreq NULL: not).      */
+int b200_pooled_merge_unrotate(void* out, int64_t ldo, const float* lse1, int64_t ld1, const float* part,
+                               int64_t ld_part, const float* lse2, int64_t ld2, const float* vfreq_hi,
+                               const float* vfreq_lo, int pairing, const int* tok_pos, const int* tok_list,
+                               int T, int H, int E, int dtype, void* stream);
+/* b200_attn_extend_window (causal) that also writes lse [token rows, lse_stride >= Hq]: log2 of every
+ * row's softmax denominator, the scaled scores taken as exponents of e.                              */
+int b200_attn_extend_lse(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                         int64_t kv_row_stride, void* o, int64_t o_stride, const int32_t* req_to_token,
+                         int64_t req_to_token_stride, const int64_t* req_pool_indices,
+                         const int64_t* seq_lens, const int32_t* extend_prefix_lens,
+                         const int32_t* extend_seq_lens, const int32_t* extend_start_loc, int bs,
+                         int max_extend_len, int Hq, int Hkv, int D, int Dv, float scale, int window,
+                         float* lse, int64_t lse_stride, int dtype, void* stream);
 /* Router with softmax scores over all experts: choice = s + correction (NULL: 0); experts in n_groups
  * groups of neighbours, only the `keep` groups with the largest choice score take part; the `top`
  * largest choice scores are chosen; weights = s of the chosen / (their sum + 1e-20).                 */

@@ -250,16 +250,29 @@ _SIGNATURES = {
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                       c_int, c_int, c_int, c_int, c_void_p]),
     "b200_delta_recurrence_state_width": (c_int64, [c_int, c_int, c_int]),
+    "b200_delta_recurrence_work_width": (c_int64, [c_int, c_int, c_int, c_int]),
     "b200_delta_recurrence": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                       c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float,
                                       c_float, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
-                                      c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
-                                      c_int, c_void_p]),
+                                      c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int,
+                                      c_int, c_int, c_int, c_void_p]),
     "b200_headnorm_rot_write": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                         c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
-                                        c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
-                                        c_void_p]),
+                                        c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_void_p]),
+    "b200_pooled_blocks_attn_part": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p,
+                                             c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p,
+                                             c_void_p, c_float, c_int, c_void_p, c_int64, c_void_p, c_int64,
+                                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                             c_void_p]),
+    "b200_pooled_merge_unrotate": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                           c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                           c_int, c_int, c_int, c_void_p]),
+    "b200_attn_extend_lse": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+                                     c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                                     c_int64, c_int, c_void_p]),
     "b200_pool_block_means": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_int, c_void_p,
                                       c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200_pooled_window_attn": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p,

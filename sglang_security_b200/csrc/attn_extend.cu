@@ -54,6 +54,9 @@ struct ExtendParams {
                                  // stay those of its own); < 0: its own key/value head's
   int64_t o_plane;               // NV > 1 (value heads v_head .. v_head + NV - 1 in one launch: one score
                                  // and softmax pass, NV products): elements between their output planes
+  float* lse;                    // optional [token rows, lse_stride >= Hq]: log2 of every row's softmax
+  int64_t lse_stride;            // denominator (scaled scores in log2 units), for merging this launch's
+                                 // normalised output with a softmax over other keys
 };
 
 constexpr int kExtThreads = 256;
@@ -450,6 +453,8 @@ attn_extend_kernel(const ExtendParams p) {
     if (p.sink && m != -INFINITY)   // m and the exponents are in log2 units
       l += fast_exp2(p.sink[head_base + r % p.pack] * 1.4426950408889634f - m);
     const float inv_l = l > 0.f ? p.out_scale / l : 0.f;
+    if (p.lse && row_ok)
+      p.lse[(q_row0 + tok) * p.lse_stride + head_base + r % p.pack] = l > 0.f ? m + log2f(l) : -INFINITY;
     T* orow = static_cast<T*>(p.o) + (q_row0 + (row_ok ? tok : 0)) * p.o_stride +
               static_cast<int64_t>(head_base + r % p.pack) * D;
 #pragma unroll 1
@@ -588,16 +593,18 @@ int b200_attn_extend_sink(const void* q, int64_t q_stride, const void* k_cache, 
                                 stream);
 }
 
-int b200_attn_extend_heads(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
-                           int64_t kv_row_stride, void* o, int64_t o_stride,
-                           const int32_t* req_to_token, int64_t req_to_token_stride,
-                           const int64_t* req_pool_indices, const int64_t* seq_lens,
-                           const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
-                           const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq, int Hkv,
-                           int D, int Dv, float scale, float logit_cap, float out_scale, int causal,
-                           int window, int keep_first, const float* sink, int v_head, int n_values,
-                           int64_t o_plane, int dtype, void* stream) {
+static int extend_heads_impl(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                             int64_t kv_row_stride, void* o, int64_t o_stride,
+                             const int32_t* req_to_token, int64_t req_to_token_stride,
+                             const int64_t* req_pool_indices, const int64_t* seq_lens,
+                             const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
+                             const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq, int Hkv,
+                             int D, int Dv, float scale, float logit_cap, float out_scale, int causal,
+                             int window, int keep_first, const float* sink, int v_head, int n_values,
+                             int64_t o_plane, float* lse, int64_t lse_stride, int dtype, void* stream) {
   using namespace b200;
+  B200_REQUIRE(!lse || (lse_stride >= Hq && !sink), "b200_attn_extend: row sums of %d heads in rows of %lld", Hq,
+               static_cast<long long>(lse_stride));
   B200_REQUIRE(keep_first >= 0 && v_head < Hkv, "b200_attn_extend: kept tokens %d, value head %d",
                keep_first, v_head);
   B200_REQUIRE(n_values == 1 || (n_values == 2 && v_head >= 0 && v_head + 2 <= Hkv && o_plane % 8 == 0),
@@ -648,6 +655,8 @@ int b200_attn_extend_heads(const void* q, int64_t q_stride, const void* k_cache,
   p.sink = sink;
   p.v_head = v_head;
   p.o_plane = o_plane;
+  p.lse = lse;
+  p.lse_stride = lse_stride;
   B200_REQUIRE(bs <= 65535 && Hkv * p.head_tiles <= 65535, "b200_attn_extend: grid too large");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == B200_BF16)
@@ -655,6 +664,35 @@ int b200_attn_extend_heads(const void* q, int64_t q_stride, const void* k_cache,
                     : launch_extend<__nv_bfloat16, 64>(p, n_values, bs, max_extend_len, st);
   return D == 128 ? launch_extend<__half, 128>(p, n_values, bs, max_extend_len, st)
                   : launch_extend<__half, 64>(p, n_values, bs, max_extend_len, st);
+}
+
+int b200_attn_extend_heads(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                           int64_t kv_row_stride, void* o, int64_t o_stride,
+                           const int32_t* req_to_token, int64_t req_to_token_stride,
+                           const int64_t* req_pool_indices, const int64_t* seq_lens,
+                           const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
+                           const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq, int Hkv,
+                           int D, int Dv, float scale, float logit_cap, float out_scale, int causal,
+                           int window, int keep_first, const float* sink, int v_head, int n_values,
+                           int64_t o_plane, int dtype, void* stream) {
+  return extend_heads_impl(q, q_stride, k_cache, v_cache, kv_row_stride, o, o_stride, req_to_token,
+                           req_to_token_stride, req_pool_indices, seq_lens, extend_prefix_lens,
+                           extend_seq_lens, extend_start_loc, bs, max_extend_len, Hq, Hkv, D, Dv, scale,
+                           logit_cap, out_scale, causal, window, keep_first, sink, v_head, n_values, o_plane,
+                           nullptr, 0, dtype, stream);
+}
+
+int b200_attn_extend_lse(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                         int64_t kv_row_stride, void* o, int64_t o_stride, const int32_t* req_to_token,
+                         int64_t req_to_token_stride, const int64_t* req_pool_indices,
+                         const int64_t* seq_lens, const int32_t* extend_prefix_lens,
+                         const int32_t* extend_seq_lens, const int32_t* extend_start_loc, int bs,
+                         int max_extend_len, int Hq, int Hkv, int D, int Dv, float scale, int window,
+                         float* lse, int64_t lse_stride, int dtype, void* stream) {
+  return extend_heads_impl(q, q_stride, k_cache, v_cache, kv_row_stride, o, o_stride, req_to_token,
+                           req_to_token_stride, req_pool_indices, seq_lens, extend_prefix_lens,
+                           extend_seq_lens, extend_start_loc, bs, max_extend_len, Hq, Hkv, D, Dv, scale, 0.f,
+                           1.f, 1, window, 0, nullptr, -1, 1, 0, lse, lse_stride, dtype, stream);
 }
 
 }  // extern "C"

@@ -23,7 +23,12 @@
 //                        per pass; warps take the visible keys (blocks first, then tokens) in tiles of
 //                        32: a lane scores one key, then the warp accumulates the tile's values, each
 //                        warp with a running maximum and sum per head, merged in warp order.  Scores,
-//                        weights, sums and the final counter-rotation are fp32.
+//                        weights, sums and the final counter-rotation are fp32.  In its `part` form it
+//                        takes the blocks only and writes the normalised fp32 sum with the log2 of its
+//                        denominator, for rows whose tokens were summed by the tensor-core kernel.
+//   pooled_merge_unrotate : for the rows of long prompt portions: out = w1 * (window part, 16-bit, from the
+//                        tcgen05 extend kernel with its row log-sums) + w2 * (block part, fp32), the weights
+//                        from the two log-sums (one softmax over both key sets), then the counter-rotation.
 #include "common.cuh"
 
 namespace b200 {
@@ -66,7 +71,8 @@ headnorm_rot_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
                           int pairing, const float* __restrict__ head_scale,
                           const int* __restrict__ tok_pos, const int64_t* __restrict__ loc,
                           T* __restrict__ pool, int64_t ld_pool, int k_off, int v_off,
-                          float* __restrict__ q_out, int64_t ldqo, int H, int G, int D, int E) {
+                          float* __restrict__ q_out, int64_t ldqo, T* __restrict__ q_out16,
+                          int64_t ldqo16, int H, int G, int D, int E) {
   extern __shared__ float pp_smem[];
   const int t = blockIdx.x, half = rot_dims / 2, vhalf = vfreq_hi ? E / 2 : 0;
   float* cs = pp_smem;              // [half]
@@ -111,8 +117,13 @@ headnorm_rot_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
       const float y = to_float<T>(row[hd * D + pd]) * r * (w ? w[pd] : 1.f);
       x = fmaf(x, cs[fi], sg * y * sn[fi]);
     }
-    if (is_q) q_out[t * ldqo + i] = head_scale ? x * head_scale[hd] : x;
-    else prow[k_off + i] = from_float<T>(x);
+    if (is_q) {
+      if (head_scale) x *= head_scale[hd];
+      q_out[t * ldqo + i] = x;
+      if (q_out16) q_out16[t * ldqo16 + i] = from_float<T>(x);
+    } else {
+      prow[k_off + i] = from_float<T>(x);
+    }
   }
   for (int i = threadIdx.x; i < G * E; i += kPoolPrepThreads) {
     const int g = i / E, d = i - g * E;
@@ -159,7 +170,9 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
                           const int* __restrict__ tok_pos, const int* __restrict__ tok_b, float scale,
                           int window, const float* __restrict__ vfreq_hi,
                           const float* __restrict__ vfreq_lo, int pairing, TO* __restrict__ out,
-                          int64_t ldo, int H, int G, int D, int E, const int* __restrict__ tok_list) {
+                          int64_t ldo, int H, int G, int D, int E, const int* __restrict__ tok_list,
+                          float* __restrict__ part_out, int64_t ld_part, float* __restrict__ part_lse,
+                          int64_t ld_lse) {
   extern __shared__ __align__(16) float pw_smem[];
   constexpr int RH = kPwHeads;
   const int nw = blockDim.x >> 5;
@@ -178,8 +191,8 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
   const int* r2t = req_to_token + req_idx[tok_b[t]] * ld_r2t;
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int npool = (pooled && P > 0) ? lo / P : 0;       // blocks that end before the window
-  const int nkeys = npool + (p - lo + 1);
-  if (vfreq_hi)
+  const int nkeys = part_out ? npool : npool + (p - lo + 1);   // the part form takes the blocks only
+  if (vfreq_hi && !part_out)
     for (int i = threadIdx.x; i < E / 2; i += blockDim.x)
       exact_sincos(static_cast<float>(p), vfreq_hi[i], vfreq_lo ? vfreq_lo[i] : 0.f, vcs + i, vsn + i);
   const bool kvec = sizeof(TP) == 2 && (D % 8 == 0) && (ld_pool % 8 == 0) && ((k_off + g * D) % 8 == 0) &&
@@ -347,9 +360,21 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
       const int r = i / E, e = i - r * E;
       float o = 0.f;
       for (int w = 0; w < nw; ++w) o = fmaf(wacc[(w * RH + r) * E + e], wf[w * RH + r], o);
-      om[i] = o / wt[r];
+      om[i] = wt[r] > 0.f ? o / wt[r] : 0.f;
     }
     __syncthreads();
+    if (part_out) {
+      // the normalised sum over the blocks and log2 of its denominator (-inf: no block in sight)
+      for (int i = threadIdx.x; i < nr * E; i += blockDim.x)
+        part_out[t * ld_part + hb * E + i] = om[i];
+      if (threadIdx.x < nr) {
+        const int r = threadIdx.x;
+        float mt = -INFINITY;
+        for (int w = 0; w < nw; ++w) mt = fmaxf(mt, wm[w * RH + r]);
+        part_lse[t * ld_lse + hb + r] = wt[r] > 0.f ? (mt + logf(wt[r])) * 1.4426950408889634f : -INFINITY;
+      }
+      continue;
+    }
     for (int i = threadIdx.x; i < nr * E; i += blockDim.x) {
       const int r = i / E, e = i - r * E;
       float o = om[i];
@@ -364,6 +389,50 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256)
+pooled_merge_unrotate_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ lse1, int64_t ld1,
+                             const float* __restrict__ part, int64_t ld_part,
+                             const float* __restrict__ lse2, int64_t ld2,
+                             const float* __restrict__ vfreq_hi, const float* __restrict__ vfreq_lo,
+                             int pairing, const int* __restrict__ tok_pos,
+                             const int* __restrict__ tok_list, int H, int E) {
+  extern __shared__ float mg_smem[];          // [H * E] merged row, [E / 2] cos, [E / 2] sin
+  float* row = mg_smem;
+  float* vcs = row + H * E;
+  float* vsn = vcs + E / 2;
+  const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x;
+  if (vfreq_hi)
+    for (int i = threadIdx.x; i < E / 2; i += blockDim.x)
+      exact_sincos(static_cast<float>(tok_pos[t]), vfreq_hi[i], vfreq_lo ? vfreq_lo[i] : 0.f, vcs + i, vsn + i);
+  for (int i = threadIdx.x; i < H * E; i += blockDim.x) {
+    const int h = i / E;
+    float o = to_float<T>(out[t * ldo + i]);
+    if (part) {
+      // both parts are normalised sums; exp2 of their log-sums are the two denominators
+      const float a = lse1[t * ld1 + h], b = lse2[t * ld2 + h];
+      if (b != -INFINITY) {
+        const float mx = fmaxf(a, b);
+        const float wa = exp2f(a - mx), wb = exp2f(b - mx);
+        o = (wa * o + wb * part[t * ld_part + i]) / (wa + wb);
+      }
+    }
+    row[i] = o;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H * E; i += blockDim.x) {
+    const int h = i / E, e = i - h * E;
+    float o = row[i];
+    if (vfreq_hi) {
+      int pd, fi;
+      float sg;
+      rot_pair(e, E, pairing, &pd, &fi, &sg);
+      o = fmaf(o, vcs[fi], -sg * row[h * E + pd] * vsn[fi]);
+    }
+    out[t * ldo + i] = from_float<T>(o);
+  }
+}
+
 }  // namespace b200
 
 extern "C" int b200_headnorm_rot_write(const void* q, int64_t ldq, const void* k, int64_t ldk,
@@ -372,8 +441,9 @@ extern "C" int b200_headnorm_rot_write(const void* q, int64_t ldq, const void* k
                                        int rot_dims, const float* vfreq_hi, const float* vfreq_lo,
                                        int pairing, const float* head_scale, const int* tok_pos,
                                        const int64_t* loc, void* pool, int64_t ld_pool, int k_off,
-                                       int v_off, float* q_out, int64_t ldqo, int T, int H, int G, int D,
-                                       int E, int dtype, void* stream) {
+                                       int v_off, float* q_out, int64_t ldqo, void* q_out16,
+                                       int64_t ldqo16, int T, int H, int G, int D, int E, int dtype,
+                                       void* stream) {
   using namespace b200;
   if (T == 0) return 0;
   B200_REQUIRE(q && k && v && tok_pos && loc && pool && q_out, "b200_headnorm_rot_write: null pointer");
@@ -391,7 +461,7 @@ extern "C" int b200_headnorm_rot_write(const void* q, int64_t ldq, const void* k
                 static_cast<const TT*>(q), ldq, static_cast<const TT*>(k), ldk,                      \
                 static_cast<const TT*>(v), ldv, qw, kw, eps, freq_hi, freq_lo, rot_dims, vfreq_hi,   \
                 vfreq_lo, pairing, head_scale, tok_pos, loc, static_cast<TT*>(pool), ld_pool, k_off, \
-                v_off, q_out, ldqo, H, G, D, E)
+                v_off, q_out, ldqo, static_cast<TT*>(q_out16), ldqo16, H, G, D, E)
   if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
   else if (dtype == B200_F16) LAUNCH(__half);
   else if (dtype == B200_F32) LAUNCH(float);
@@ -425,18 +495,20 @@ extern "C" int b200_pool_block_means(const void* pool, int64_t ld_pool, int widt
   return 0;
 }
 
-extern "C" int b200_pooled_window_attn(const float* q, int64_t ldq, const void* pool, int64_t ld_pool,
-                                       int k_off, int v_off, const float* pooled, int64_t ld_pooled,
-                                       int P, int pdiv, const int* req_to_token, int64_t ld_r2t,
-                                       const int64_t* req_idx, const int* tok_pos, const int* tok_b,
-                                       float scale, int window, const float* vfreq_hi,
-                                       const float* vfreq_lo, int pairing, void* out, int64_t ldo, int T,
-                                       int H, int G, int D, int E, const int* tok_list, int max_keys,
-                                       int dtype, void* stream) {
+static int pooled_window_attn_impl(const float* q, int64_t ldq, const void* pool, int64_t ld_pool,
+                                   int k_off, int v_off, const float* pooled, int64_t ld_pooled, int P,
+                                   int pdiv, const int* req_to_token, int64_t ld_r2t,
+                                   const int64_t* req_idx, const int* tok_pos, const int* tok_b,
+                                   float scale, int window, const float* vfreq_hi, const float* vfreq_lo,
+                                   int pairing, void* out, int64_t ldo, int T, int H, int G, int D, int E,
+                                   const int* tok_list, int max_keys, float* part_out, int64_t ld_part,
+                                   float* part_lse, int64_t ld_lse, int dtype, void* stream) {
   using namespace b200;
   if (T == 0) return 0;
-  B200_REQUIRE(q && pool && req_to_token && req_idx && tok_pos && tok_b && out,
+  B200_REQUIRE(q && pool && req_to_token && req_idx && tok_pos && tok_b && (out || part_out),
                "b200_pooled_window_attn: null pointer");
+  B200_REQUIRE(!part_out || (part_lse && pooled && ld_part >= static_cast<int64_t>(H) * E && ld_lse >= H),
+               "b200_pooled_window_attn: the block part needs its buffers and a summary");
   B200_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && E > 0 && E <= 32 * kPwMaxCols &&
                    window >= 0 && G <= 65535 && (!pooled || (P > 0 && window > 0 && (pdiv == 1 || pdiv == P))) &&
                    (!vfreq_hi || E % 2 == 0),
@@ -457,12 +529,67 @@ extern "C" int b200_pooled_window_attn(const float* q, int64_t ldq, const void* 
   launch_kernel(pooled_window_attn_kernel<TT, TT>, grid, dim3(nw * 32), smem, st, 1, 0, q, ldq,      \
                 static_cast<const TT*>(pool), ld_pool, k_off, v_off, pooled, ld_pooled, P, pdiv,     \
                 req_to_token, ld_r2t, req_idx, tok_pos, tok_b, scale, window, vfreq_hi, vfreq_lo,    \
-                pairing, static_cast<TT*>(out), ldo, H, G, D, E, tok_list)
+                pairing, static_cast<TT*>(out), ldo, H, G, D, E, tok_list, part_out, ld_part, part_lse,   \
+                ld_lse)
   if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
   else if (dtype == B200_F16) LAUNCH(__half);
   else if (dtype == B200_F32) LAUNCH(float);
   else B200_REQUIRE(false, "b200_pooled_window_attn: dtype %d", dtype);
 #undef LAUNCH
   B200_CHECK_LAUNCH("pooled_window_attn_kernel");
+  return 0;
+}
+
+extern "C" int b200_pooled_window_attn(const float* q, int64_t ldq, const void* pool, int64_t ld_pool,
+                                       int k_off, int v_off, const float* pooled, int64_t ld_pooled,
+                                       int P, int pdiv, const int* req_to_token, int64_t ld_r2t,
+                                       const int64_t* req_idx, const int* tok_pos, const int* tok_b,
+                                       float scale, int window, const float* vfreq_hi,
+                                       const float* vfreq_lo, int pairing, void* out, int64_t ldo, int T,
+                                       int H, int G, int D, int E, const int* tok_list, int max_keys,
+                                       int dtype, void* stream) {
+  return pooled_window_attn_impl(q, ldq, pool, ld_pool, k_off, v_off, pooled, ld_pooled, P, pdiv,
+                                 req_to_token, ld_r2t, req_idx, tok_pos, tok_b, scale, window, vfreq_hi,
+                                 vfreq_lo, pairing, out, ldo, T, H, G, D, E, tok_list, max_keys, nullptr, 0,
+                                 nullptr, 0, dtype, stream);
+}
+
+extern "C" int b200_pooled_blocks_attn_part(const float* q, int64_t ldq, const void* pool, int64_t ld_pool,
+                                            int k_off, int v_off, const float* pooled, int64_t ld_pooled,
+                                            int P, int pdiv, const int* req_to_token, int64_t ld_r2t,
+                                            const int64_t* req_idx, const int* tok_pos, const int* tok_b,
+                                            float scale, int window, float* part_out, int64_t ld_part,
+                                            float* part_lse, int64_t ld_lse, int T, int H, int G, int D,
+                                            int E, const int* tok_list, int max_keys, int dtype,
+                                            void* stream) {
+  return pooled_window_attn_impl(q, ldq, pool, ld_pool, k_off, v_off, pooled, ld_pooled, P, pdiv,
+                                 req_to_token, ld_r2t, req_idx, tok_pos, tok_b, scale, window, nullptr,
+                                 nullptr, 0, nullptr, 0, T, H, G, D, E, tok_list, max_keys, part_out,
+                                 ld_part, part_lse, ld_lse, dtype, stream);
+}
+
+extern "C" int b200_pooled_merge_unrotate(void* out, int64_t ldo, const float* lse1, int64_t ld1,
+                                          const float* part, int64_t ld_part, const float* lse2,
+                                          int64_t ld2, const float* vfreq_hi, const float* vfreq_lo,
+                                          int pairing, const int* tok_pos, const int* tok_list, int T,
+                                          int H, int E, int dtype, void* stream) {
+  using namespace b200;
+  if (T == 0) return 0;
+  B200_REQUIRE(out && tok_pos && T > 0 && H > 0 && E > 0 && (!part || (lse1 && lse2)) &&
+                   (!vfreq_hi || E % 2 == 0) && (pairing == 0 || pairing == 1),
+               "b200_pooled_merge_unrotate: bad arguments");
+  const size_t smem = sizeof(float) * (static_cast<size_t>(H) * E + E + 2);
+  B200_REQUIRE(smem <= 48 * 1024, "b200_pooled_merge_unrotate: %d heads of %d values", H, E);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("pooled_merge_unrotate", st);
+#define LAUNCH(TT)                                                                                   \
+  launch_kernel(pooled_merge_unrotate_kernel<TT>, dim3(T), dim3(256), smem, st, 1, 0,               \
+                static_cast<TT*>(out), ldo, lse1, ld1, part, ld_part, lse2, ld2, vfreq_hi, vfreq_lo, \
+                pairing, tok_pos, tok_list, H, E)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else B200_REQUIRE(false, "b200_pooled_merge_unrotate: dtype %d", dtype);
+#undef LAUNCH
+  B200_CHECK_LAUNCH("pooled_merge_unrotate_kernel");
   return 0;
 }

@@ -63,13 +63,17 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_ra
             raise _lib.B200Error("delta_recurrence: inputs need contiguous rows of one dtype")
     T = q.shape[0]
     out = torch.empty((T, heads * vdim), dtype=torch.float32, device=q.device)
-    rc = _lib.load().b200_delta_recurrence(
+    mode = 0 if beta_raw is not None else 1
+    lib = _lib.load()
+    work = torch.empty(T * int(lib.b200_delta_recurrence_work_width(heads, groups, dim, mode)),
+                       dtype=torch.float32, device=q.device)
+    rc = lib.b200_delta_recurrence(
         q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
         decay_raw.data_ptr(), decay_raw.stride(0), decay_bias.data_ptr(), a_log.data_ptr(),
         _lib.ptr(beta_raw), beta_raw.stride(0) if beta_raw is not None else 0, _lib.ptr(skip),
-        float(q_scale), float(unit_eps), 0 if beta_raw is not None else 1, state.data_ptr(), state.stride(0),
+        float(q_scale), float(unit_eps), mode, state.data_ptr(), state.stride(0),
         fb.req_pool_indices.data_ptr(), fb.tok_pos.data_ptr(), fb.ext_start.data_ptr(), fb.ext_len.data_ptr(),
-        out.data_ptr(), out.stride(0), int(fb.batch_size), heads, groups, dim, vdim,
+        out.data_ptr(), out.stride(0), work.data_ptr(), T, int(fb.batch_size), heads, groups, dim, vdim,
         _lib.dtype_code(q.dtype), _lib.current_stream())
     _lib.check(rc, "b200_delta_recurrence")
     return out

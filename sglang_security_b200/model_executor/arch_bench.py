@@ -1,8 +1,10 @@
-"""Prefill and decode throughput of the Desirax, Dozetar and Kulesun designs at layer sizes that resemble
+"""Prefill and decode throughput of the Desirax, Dozetar, Kulesun and Kisilix designs at layer sizes that resemble
 a real model's, beside the Llama-family decoder stack of this package at equal width / heads / head size /
 layer count and equal active feed-forward size (random weights, bf16).  Driven by
 `bench.py --arch-compare` (sizes named "dz-..." are Dozetar's, "ku-..." Kulesun's; a Kulesun size also
-runs the Desirax stack, its closest relative, at equal width, heads, latent sizes, layers and feed-forward).
+runs the Desirax stack, its closest relative, at equal width, heads, latent sizes, layers and feed-forward;
+"ki-..." are Kisilix's, which also run the Dozetar stack — recurrent memories of the same shape, windowed
+attention with the same heads, experts of the same size).
 
 Timing: CUDA events on the launching stream around whole engine steps, after warm-up steps; every step
 touches more weight and cache bytes than L2 holds at the larger size.  Per-kernel times come from the
@@ -44,6 +46,13 @@ KULESUN_SIZES = {
                      vdim=128, kv_rank=256, q_rank=384, window=1 << 20, ff=4096, moe=None, rot_llama=64),
     "ku-w2048": dict(width=2048, layers=4, vocab=32000, heads=16, kv_heads=2, adim=128, avdim=128, dim=64, rot=64,
                      vdim=128, kv_rank=512, q_rank=768, window=1 << 20, ff=8192, moe=None, rot_llama=64),
+}
+# Kisilix: delta rule, attention (window + pooled blocks), state space, attention; experts with a shared
+# expert in every layer.  The memories have the shapes of the Dozetar row's (mlstm = delta rule, decayed =
+# state space), the attention its heads, the experts its sizes.
+KISILIX_SIZES = {
+    "ki-w1024": dict(DOZETAR_SIZES["dz-w1024"], pool=64, conv=4, rank=64, groups=4, keep=2, shared=1024),
+    "ki-w2048": dict(DOZETAR_SIZES["dz-w2048"], pool=64, conv=4, rank=128, groups=4, keep=2, shared=1024),
 }
 WORK = dict(prefill_reqs=4, prefill_len=2048, decode_bs=32, decode_ctx=2048)
 
@@ -400,6 +409,118 @@ def bench_kulesun(name, s, steps, warmup, device="cuda"):
     return row
 
 
+def _kisilix_cfg(s):
+    delta = {"type": "channel_delta", "mixer": {"heads": s["m_heads"], "kv_heads": s["m_heads"], "dim": s["m_dim"],
+                                                "vdim": s["m_vdim"], "conv": s["conv"]}}
+    ssm = {"type": "mamba2", "mixer": {"heads": s["r_heads"], "vdim": s["r_vdim"], "state": s["r_dim"], "groups": 1,
+                                       "norm_groups": 1, "conv": s["conv"]}}
+    att = {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"],
+                                          "vdim": s["vdim"], "scale": s["dim"] ** -0.5,
+                                          "mask": {"size": s["window"], "pool": s["pool"]},
+                                          "rot": {"base": 1e6, "dims": s["rot"]}}}
+    f = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"],
+                                   "groups": {"count": s["groups"], "keep": s["keep"]}},
+         "expert": {"ff": s["expert_ff"]}, "shared": {"ff": s["shared"]}}
+    order = [delta, att, ssm, att]
+    return {"architecture": "Kisilix", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "postln_alpha": 2.0, "max_positions": 4096,
+            "layers": [dict(order[i % 4], mlp=f) for i in range(s["layers"])]}
+
+
+def bench_kisilix(name, s, steps, warmup, device="cuda"):
+    from ..configs.kisilix import kisilix_config
+    from ..managers.schedule_batch import Req, StepItem
+    from ..managers.scheduler import Scheduler
+    from ..models.registry import resolve_model_cls
+    from .model_runner import ModelRunner
+
+    cfg = kisilix_config(_kisilix_cfg(s))
+    for L in cfg.layers:
+        if L.type == "channel_delta":
+            L.mixer.decay_rank = L.mixer.gate_rank = s["rank"]
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = resolve_model_cls("Kisilix")(cfg, params_dtype=torch.bfloat16)
+    for n_, p in model.named_parameters():
+        if n_.endswith("norm_weight") or n_.endswith("norm1.weight") or n_.endswith("norm2.weight") or \
+                n_.endswith("final_norm.weight") or n_.endswith("head_scale"):
+            p.data.fill_(1.0)
+        elif n_.endswith("bias") or n_.endswith("correction") or n_.endswith("a_log") or n_.endswith("skip"):
+            p.data.zero_()
+        elif n_.endswith("conv_weight"):
+            p.data.normal_(0, 0.5)
+        else:
+            p.data.normal_(0, 0.02)
+    W = WORK
+    bs = max(W["prefill_reqs"], W["decode_bs"])
+    tokens = W["decode_bs"] * (W["decode_ctx"] + 64) + W["prefill_reqs"] * W["prefill_len"]
+    runner = ModelRunner(None, torch.bfloat16, max_total_tokens=tokens, max_running_requests=bs + 1,
+                         context_length=max(W["prefill_len"], W["decode_ctx"] + 64), device=device,
+                         model=model.eval(), model_config=SimpleNamespace(architecture="Kisilix", hf_config=cfg))
+    sched = Scheduler(runner)
+    g = torch.Generator().manual_seed(1)
+    rnd = lambda n: torch.randint(0, s["vocab"], (n,), generator=g).tolist()
+
+    def prefill():
+        reqs = [Req(rid=f"p{i}", input_ids=rnd(W["prefill_len"])) for i in range(W["prefill_reqs"])]
+        for r in reqs:
+            assert runner.admit(r)
+        sched.run_step([StepItem(r, r.input_ids, want=[len(r.input_ids) - 1]) for r in reqs])
+        for r in reqs:
+            runner.release(r)
+
+    names = ["delta_recurrence", "ssm_recurrence", "causal_conv_silu", "gated_group_rmsnorm", "pooled_window_attn",
+             "attn_extend", "headnorm_rot_write", "pool_block_means", "moe_grouped_gemm", "moe_route", "moe_align",
+             "scaled_add_layernorm", "act_and_mul"]
+    row = {"arch": "kisilix", "size": name}
+    ms = _timed(prefill, steps, warmup)
+    ntok = W["prefill_reqs"] * W["prefill_len"]
+    row["prefill_ms"], row["prefill_tokens_per_s"] = round(ms, 3), round(ntok / ms * 1e3)
+    row["prefill_kernels"] = _kernel_times(prefill, names)
+    reqs = [Req(rid=f"d{i}", input_ids=rnd(W["decode_ctx"])) for i in range(W["decode_bs"])]
+    for r in reqs:
+        assert runner.admit(r)
+    for i in range(0, len(reqs), 4):
+        sched.run_step([StepItem(r, r.input_ids) for r in reqs[i:i + 4]])
+    state = {"n": 0}
+
+    def decode():
+        state["n"] += 1
+        assert state["n"] < 60
+        sched.run_step([StepItem(r, [7], want=[0]) for r in reqs])
+
+    ms = _timed(decode, steps, warmup)
+    row["decode_ms"], row["decode_tokens_per_s"] = round(ms, 3), round(W["decode_bs"] / ms * 1e3)
+    row["decode_kernels"] = _kernel_times(decode, names)
+
+    def mixed():
+        state["n"] += 1
+        assert state["n"] < 60
+        new = Req(rid=f"m{state['n']}", input_ids=rnd(512))
+        assert runner.admit(new)
+        sched.run_step([StepItem(r, [7], want=[0]) for r in reqs] + [StepItem(new, new.input_ids, want=[511])])
+        runner.release(new)
+
+    row["mixed_ms"] = round(_timed(mixed, min(steps, 8), 3), 3)
+    # algorithmic work of one launch (all tokens, one layer)
+    L, U = W["prefill_len"], W["prefill_reqs"]
+    vis = lambda p: min(p + 1, s["window"]) + max(0, p + 1 - s["window"]) // s["pool"]
+    keys = sum(vis(p) for p in range(L)) * U
+    row["attn_prefill_flops"] = 2 * keys * s["heads"] * (s["dim"] + s["vdim"])
+    row["attn_decode_bytes"] = W["decode_bs"] * (min(W["decode_ctx"] + 1, s["window"]) * 2 + (
+        max(0, W["decode_ctx"] + 1 - s["window"]) // s["pool"]) * 4) * s["kv_heads"] * (s["dim"] + s["vdim"])
+    # recurrences: fp32 multiply-adds per memory element and token: the delta rule has four (decay, S^T k,
+    # the write, the read-out), the state-space form three; a decoded token reads and writes its memory once
+    row["delta_prefill_fma"] = 4 * U * L * s["m_heads"] * s["m_dim"] * s["m_vdim"]
+    row["ssm_prefill_fma"] = 3 * U * L * s["r_heads"] * s["r_dim"] * s["r_vdim"]
+    row["delta_decode_bytes"] = 2 * 4 * W["decode_bs"] * s["m_heads"] * s["m_dim"] * s["m_vdim"]
+    row["ssm_decode_bytes"] = 2 * 4 * W["decode_bs"] * s["r_heads"] * s["r_dim"] * s["r_vdim"]
+    row["expert_prefill_flops"] = 2 * 3 * U * L * s["top"] * s["expert_ff"] * s["width"]
+    del runner, sched, model
+    torch.cuda.empty_cache()
+    return row
+
+
 def bench_llama_like(name, s, steps, warmup, device="cuda"):
     """The package's Llama-family stack (B200DecoderLayer: fused RMSNorm, rotary + KV write, paged
     attention, gated silu MLP) at the same width, heads, head size 128, layers, GQA 4:1, bf16."""
@@ -462,10 +583,13 @@ def bench_llama_like(name, s, steps, warmup, device="cuda"):
 
 def run(steps: int, warmup: int, sizes=None):
     rows = []
-    for name, s in list(SIZES.items()) + list(DOZETAR_SIZES.items()) + list(KULESUN_SIZES.items()):
+    every = list(SIZES.items()) + list(DOZETAR_SIZES.items()) + list(KULESUN_SIZES.items()) + list(KISILIX_SIZES.items())
+    for name, s in every:
         if sizes and name not in sizes:
             continue
-        if name in KULESUN_SIZES:
+        if name in KISILIX_SIZES:
+            fns = (bench_kisilix, bench_dozetar, bench_llama_like)
+        elif name in KULESUN_SIZES:
             fns = (bench_kulesun, bench_desirax, bench_llama_like)
         else:
             fns = ((bench_dozetar if name in DOZETAR_SIZES else bench_desirax), bench_llama_like)

@@ -132,14 +132,14 @@ def _run_recurrence(mode, H, G, D, E, dtype, lens, sizes, seed, state=None, hb=N
     g = _gen(seed)
     rows = rows or list(range(len(lens)))
     nd = H * D if mode == "delta" else H
+    bias, a_log = torch.randn(nd, generator=g) - 1.0, 0.7 * torch.randn(H, generator=g) - 0.5
+    skip = torch.randn(H, generator=g)
     seqs = {}
     for r, n in zip(rows, lens):
         seqs[r] = dict(q=torch.randn(n, G * D, generator=g).to(dtype), k=torch.randn(n, G * D, generator=g).to(dtype),
                        v=torch.randn(n, H * E, generator=g).to(dtype),
                        d=(1.5 * torch.randn(n, nd, generator=g)).to(dtype),
                        b=(1.5 * torch.randn(n, H, generator=g)).to(dtype))
-    bias, a_log = torch.randn(nd, generator=g) - 1.0, 0.7 * torch.randn(H, generator=g) - 0.5
-    skip = torch.randn(H, generator=g)
     if state is None:
         state = torch.full((max(rows) + 2, H * D * E + 5), 3.0, device=DEV)     # stale values
         hb = U.HandBatch(max(rows) + 2, 512)

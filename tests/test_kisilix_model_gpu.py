@@ -34,6 +34,13 @@ CONFIGS = {
                            (U.delta(heads=1, kv_heads=1, dim=40, vdim=70, conv=3, ranks=(5, 7)), None),
                            (U.ssm(heads=2, vdim=9, state=72, groups=2, norm_groups=3, conv=5), None)],
                           vocab=33, width=24, alpha=5.0),
+    # attention sizes the tensor-core kernel takes (key size = value size = 64 / 128), 4 : 1 and 1 : 1, with
+    # and without blocks, with and without a window
+    "d": lambda: U.config([(U.attn(heads=4, kv_heads=1, dim=64, vdim=64, window=50, pool=8, rot_dims=32), U.dense(32)),
+                           (U.ssm(heads=2, vdim=16, state=16, groups=1, norm_groups=1), None),
+                           (U.attn(heads=2, kv_heads=2, dim=128, vdim=128, window=70, pool=0, rot_dims=128), None),
+                           (U.attn(heads=2, kv_heads=1, dim=64, vdim=64, window=None, pool=0, rot_dims=64), None)],
+                          vocab=101, width=64),
     # recurrent layers only (no token pool rows at all)
     "f": lambda: U.config([(U.ssm(), U.dense()), (U.delta(), None)], vocab=61, width=32),
     # attention only
@@ -66,7 +73,7 @@ TOL_SHARP = {torch.float32: 1e-3, torch.bfloat16: 0.3}
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("name", ["a", "b", "c", "f", "g"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "f", "g"])
 def test_whole_prompt_matches_plain_model(tmp_path, name, dtype):
     cfg, w, folder = _model(tmp_path, name)
     toks = _tokens(cfg, 150, 1)
@@ -175,6 +182,35 @@ def test_batch_does_not_change_a_request_fp32(tmp_path):
     both.step([("b", b[:30]), ("a", a[:50])])
     both.step([("a", a[50:]), ("b", b[30:31])])
     assert (alone.result("a") - both.result("a")).abs().max() <= 1e-4
+
+
+@pytest.mark.parametrize("sharp", [0.0, 2.0])
+def test_long_portions_on_the_tensor_core_kernel_beside_decoded_tokens(tmp_path, monkeypatch, sharp):
+    """Portions of 16 tokens and more take the tcgen05 kernel for the window, the CUDA-core kernel for the
+    blocks and the joining launch; shorter ones and decoded tokens the CUDA-core kernel alone, in the same
+    step; every cut must give the whole prompt's logits."""
+    from sglang_security_b200.layers.attention.pooled_window_attention import PooledWindowAttention
+
+    monkeypatch.setattr(PooledWindowAttention, "tensor_core_min_tokens", 16)
+    cfg, w, folder = _model(tmp_path, "d", sharp=sharp)
+    a, b = _tokens(cfg, 300, 40), _tokens(cfg, 170, 41)
+    want_a, want_b = P.forward(cfg, w, a), P.forward(cfg, w, b)
+    tol = (TOL_SHARP if sharp else TOL)[torch.bfloat16]
+    d = U.Driver(folder, torch.bfloat16)
+    d.step([("a", a)], end=["a"])
+    assert U.rel_err(d.result("a"), want_a, torch.bfloat16) <= tol
+    d = U.Driver(folder, torch.bfloat16)
+    d.step([("a", a[:130]), ("b", b[:5])])
+    d.step([("a", a[130:131]), ("b", b[5:150])])
+    d.step([("a", a[131:290]), ("b", b[150:151])])
+    d.step([("a", a[290:]), ("b", b[151:])])
+    err_a, err_b = U.rel_err(d.result("a"), want_a, torch.bfloat16), U.rel_err(d.result("b"), want_b, torch.bfloat16)
+    assert err_a <= tol and err_b <= tol
+    monkeypatch.setattr(PooledWindowAttention, "tensor_core_min_tokens", 0)    # the CUDA-core kernel alone agrees
+    d = U.Driver(folder, torch.bfloat16)
+    d.step([("a", a)], end=["a"])
+    core = U.rel_err(d.result("a"), want_a, torch.bfloat16)
+    assert core <= tol and err_a <= 2.0 * core + 0.02        # the divided step is as close to the oracle
 
 
 def test_long_decoding(tmp_path):
