@@ -91,6 +91,10 @@ class KisilixConfig:
                     if name not in shapes:
                         raise ValueError(f"checkpoint lacks {name}")
                     setattr(L.mixer, attr, int(shapes[name][0]))
+            # the taps of a convolution are its tensor's second size
+            conv = {"channel_delta": f"l{i}.mix.q.conv", "mamba2": f"l{i}.mix.conv"}.get(L.type)
+            if conv in shapes and len(shapes[conv]) == 2:
+                L.mixer.conv = int(shapes[conv][1])
 
 
 def _heads(m: dict, key: str = "kv_heads"):

@@ -173,6 +173,17 @@ delta_recurrence_kernel(const DeltaArgs a) {
   for (int i = tid; i < 2 * buf_floats; i += nt) dr_smem[i] = 0.f;
   __syncthreads();
   const bool vec4 = (D % 4 == 0);              // the workspace rows then start on 16-byte boundaries
+  // how this CTA's slice of a value row can be copied: every piece must start on a multiple of its size
+  // in global and in shared memory and the slice must be whole pieces
+  int v_mode = 0;
+  {
+    const int c0 = blockIdx.z * cols, nc = min(cols, E - c0);
+    const uintptr_t first = reinterpret_cast<uintptr_t>(vg + h * E + c0);
+    const size_t row_bytes = static_cast<size_t>(a.ldv) * sizeof(T), slice = nc * sizeof(T),
+                 srow_bytes = cols * sizeof(T);
+    if (first % 16 == 0 && row_bytes % 16 == 0 && slice % 16 == 0 && srow_bytes % 16 == 0 && CH % 2 == 0) v_mode = 16;
+    else if (first % 4 == 0 && row_bytes % 4 == 0 && slice % 4 == 0 && srow_bytes % 4 == 0) v_mode = 4;
+  }
 
   auto stage = [&](int t0, float* buf) {
     const int m = min(CH, n - t0);
@@ -203,9 +214,23 @@ delta_recurrence_kernel(const DeltaArgs a) {
       cp_async4(smem_u32(bs + tt), a.ab + row * 2 * H + h);
       cp_async4(smem_u32(as + tt), a.ab + row * 2 * H + H + h);
     }
-    for (int idx = tid; idx < m * cols; idx += nt) {       // values: plain loads (any alignment, any type)
-      const int tt = idx / cols, cl = idx - tt * cols, ee = blockIdx.z * cols + cl;
-      vs[idx] = ee < E ? to_float<T>(vg[(row0 + t0 + tt) * a.ldv + h * E + ee]) : 0.f;
+    // values stay in their own type (converted where they are used): 16-byte or 4-byte asynchronous copies
+    // when the slice of the row allows it, plain loads otherwise
+    T* vraw = reinterpret_cast<T*>(vs);
+    const int c0 = blockIdx.z * cols, nc = min(cols, E - c0);
+    if (v_mode == 16 || v_mode == 4) {
+      const int per_v = static_cast<int>(v_mode / sizeof(T)), pieces = nc / per_v;
+      for (int idx = tid; idx < m * pieces; idx += nt) {
+        const int tt = idx / pieces, cl = (idx - tt * pieces) * per_v;
+        const T* src = vg + (row0 + t0 + tt) * a.ldv + h * E + c0 + cl;
+        if (v_mode == 16) cp_async16(smem_u32(vraw + tt * cols + cl), src);
+        else cp_async4(smem_u32(vraw + tt * cols + cl), src);
+      }
+    } else {
+      for (int idx = tid; idx < m * nc; idx += nt) {
+        const int tt = idx / nc, cl = idx - tt * nc;
+        vraw[tt * cols + cl] = vg[(row0 + t0 + tt) * a.ldv + h * E + c0 + cl];
+      }
     }
     cp_async_commit();
   };
@@ -233,10 +258,10 @@ delta_recurrence_kernel(const DeltaArgs a) {
     const float* gs = qs + CH * Dp;
     const float* bs = buf + CH * Dp * (DELTA ? 3 : 2);
     const float* as = bs + CH;
-    const float* vs = as + CH;
+    const T* vs = reinterpret_cast<const T*>(as + CH);
 #pragma unroll 1
     for (int tt = 0; tt < m; ++tt) {
-      const float vt = vs[tt * cols + tid / LPC];
+      const float vt = live ? to_float<T>(vs[tt * cols + tid / LPC]) : 0.f;
       const float* kt = ks + tt * Dp + part;
       const float* qt = qs + tt * Dp + part;
       float u;

@@ -29,6 +29,8 @@
 //   pooled_merge_unrotate : for the rows of long prompt portions: out = w1 * (window part, 16-bit, from the
 //                        tcgen05 extend kernel with its row log-sums) + w2 * (block part, fp32), the weights
 //                        from the two log-sums (one softmax over both key sets), then the counter-rotation.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -157,6 +159,51 @@ pool_block_means_kernel(const T* __restrict__ pool, int64_t ld_pool, int width,
   }
 }
 
+// acc[r][4 c + k] += weight_r(key) * row(key)[col_off + 128 c + 4 lane + k] over the `cnt` keys of a tile
+// whose rows are row_index(lane) of `base`; weights and row indices are held one key per lane.
+template <typename TR, int RH>
+__device__ __forceinline__ void accumulate_rows(const TR* __restrict__ base, int64_t ld, int col_off, int E,
+                                                int cnt, int64_t rowi, const float (&pj)[RH],
+                                                float (&acc)[RH][8], int lane) {
+  using V4 = typename std::conditional<sizeof(TR) == 2, uint2, float4>::type;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    if (128 * c >= E) continue;                // the same for all lanes: they shuffle together below
+    const int e = 128 * c + 4 * lane;
+    const bool col_ok = e < E;
+    for (int j0 = 0; j0 < cnt; j0 += 8) {
+      V4 u[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int64_t ri = __shfl_sync(0xffffffffu, rowi, (j0 + i) & 31);   // lanes past cnt hold row 0
+        u[i] = *reinterpret_cast<const V4*>(base + ri * ld + col_off + (col_ok ? e : 0));
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float x[4];
+        if constexpr (sizeof(TR) == 2) {
+          const TR* t4 = reinterpret_cast<const TR*>(&u[i]);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) x[k4] = to_float<TR>(t4[k4]);
+        } else {
+          const float* f4 = reinterpret_cast<const float*>(&u[i]);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) x[k4] = f4[k4];
+        }
+        const bool live = col_ok && j0 + i < cnt;
+#pragma unroll
+        for (int r = 0; r < RH; ++r) {
+          const float pw = __shfl_sync(0xffffffffu, pj[r], (j0 + i) & 31);
+          if (live) {
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) acc[r][4 * c + k4] = fmaf(pw, x[k4], acc[r][4 * c + k4]);
+          }
+        }
+      }
+    }
+  }
+}
+
 constexpr int kPwMaxWarps = 16;
 constexpr int kPwMaxCols = 8;     // value size <= 256
 constexpr int kPwHeads = 4;       // query heads of a key/value head scored per pass
@@ -191,7 +238,12 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
   const int* r2t = req_to_token + req_idx[tok_b[t]] * ld_r2t;
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int npool = (pooled && P > 0) ? lo / P : 0;       // blocks that end before the window
-  const int nkeys = part_out ? npool : npool + (p - lo + 1);   // the part form takes the blocks only
+  const int ntok = part_out ? 0 : p - lo + 1;                  // the part form takes the blocks only
+  const int pool_tiles = (npool + 31) >> 5, tok_tiles = (ntok + 31) >> 5;
+  if (part_out && npool == 0) {                // no block in sight: nothing to add to the window's part
+    for (int i = threadIdx.x; i < R; i += blockDim.x) part_lse[t * ld_lse + g * R + i] = -INFINITY;
+    return;
+  }
   if (vfreq_hi && !part_out)
     for (int i = threadIdx.x; i < E / 2; i += blockDim.x)
       exact_sincos(static_cast<float>(p), vfreq_hi[i], vfreq_lo ? vfreq_lo[i] : 0.f, vcs + i, vsn + i);
@@ -199,6 +251,10 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
                     ((reinterpret_cast<uintptr_t>(pool) & 15) == 0);
   const bool pvec = (D % 4 == 0) && (ld_pooled % 4 == 0) && ((k_off + g * D) % 4 == 0) &&
                     ((reinterpret_cast<uintptr_t>(pooled) & 15) == 0);
+  // values in vector loads when every piece of both buffers is aligned (one column layout for both)
+  const bool vblk = (E % 4 == 0) && (ld_pool % 4 == 0) && ((v_off + g * E) % 4 == 0) &&
+                    ((reinterpret_cast<uintptr_t>(pool) & 15) == 0) &&
+                    (!pooled || ((ld_pooled % 4 == 0) && (reinterpret_cast<uintptr_t>(pooled) & 15) == 0));
   for (int h0 = 0; h0 < R; h0 += RH) {
     const int nr = min(RH, R - h0), hb = g * R + h0;
     __syncthreads();
@@ -215,14 +271,19 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
 #pragma unroll
       for (int c = 0; c < kPwMaxCols; ++c) acc[r][c] = 0.f;
     }
-    for (int n0 = warp * 32; n0 < nkeys; n0 += nw * 32) {
-      const int n = n0 + lane;
+    // blocks and tokens are walked in tiles of 32 that never mix the two (the blocks' last tile may be
+    // partly filled), so a tile's rows have one type and one buffer
+    for (int tile = warp; tile < pool_tiles + tok_tiles; tile += nw) {
+      const bool is_pool = tile < pool_tiles;
+      const int n = (is_pool ? tile : tile - pool_tiles) * 32 + lane;      // index within its kind
+      const int cnt = min(32, (is_pool ? npool : ntok) - (n - lane));
+      const bool have = lane < cnt;
       int64_t rowi = 0;                         // pool slot, or row of the summary buffer
       float s[RH];
 #pragma unroll
       for (int r = 0; r < RH; ++r) s[r] = 0.f;
-      if (n < nkeys) {
-        if (n < npool) {
+      if (have) {
+        if (is_pool) {
           rowi = r2t[n * P + P - 1] / pdiv;
           const float* kp = pooled + rowi * ld_pooled + k_off + g * D;
           if (pvec) {
@@ -245,10 +306,11 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
             }
           }
         } else {
-          rowi = r2t[lo + (n - npool)];
+          rowi = r2t[lo + n];
           const TP* kr = pool + rowi * ld_pool + k_off + g * D;
           bool done = false;
           if constexpr (sizeof(TP) == 2) {
+#pragma unroll 2
             for (int d = 0; kvec && d < D; d += 8) {
               const uint4 u = *reinterpret_cast<const uint4*>(kr + d);
               const TP* e8 = reinterpret_cast<const TP*>(&u);
@@ -283,13 +345,13 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
       float pj[RH];
 #pragma unroll
       for (int r = 0; r < RH; ++r) {
-        const float sr = n < nkeys ? s[r] : -INFINITY;
+        const float sr = have ? s[r] : -INFINITY;
         float tm = sr;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, o));
         const float mn = fmaxf(m[r], tm);
         const float corr = expf(m[r] - mn);
-        pj[r] = n < nkeys ? expf(sr - mn) : 0.f;
+        pj[r] = have ? expf(sr - mn) : 0.f;
         float ps = pj[r];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
@@ -298,33 +360,25 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
 #pragma unroll
         for (int c = 0; c < kPwMaxCols; ++c) acc[r][c] *= corr;
       }
-      const int cnt = min(32, nkeys - n0);
-      // values: a lane owns the columns lane + 32 c; the rows of 4 keys are requested before the first is used
-      for (int j0 = 0; j0 < cnt; j0 += 4) {
-        float x[4][kPwMaxCols];
+      if (vblk) {
+        // a lane owns 4 consecutive columns per 128: one 8-byte (16-bit rows) or 16-byte (fp32 rows) load
+        // per key; the rows of 8 keys are requested before the first is used
+        if (is_pool) accumulate_rows<float, RH>(pooled, ld_pooled, v_off + g * E, E, cnt, rowi, pj, acc, lane);
+        else accumulate_rows<TP, RH>(pool, ld_pool, v_off + g * E, E, cnt, rowi, pj, acc, lane);
+      } else {
+        for (int jj = 0; jj < cnt; ++jj) {
+          const int64_t ri = __shfl_sync(0xffffffffu, rowi, jj);
+          float pw[RH];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int64_t ri = __shfl_sync(0xffffffffu, rowi, (j0 + i) & 31);
-          const bool okk = j0 + i < cnt;
-          const bool is_pool = n0 + j0 + i < npool;
+          for (int r = 0; r < RH; ++r) pw[r] = __shfl_sync(0xffffffffu, pj[r], jj);
 #pragma unroll
           for (int c = 0; c < kPwMaxCols; ++c) {
             const int e = lane + 32 * c;
-            float val = 0.f;
-            if (okk && e < E)
-              val = is_pool ? pooled[ri * ld_pooled + v_off + g * E + e]
-                            : to_float<TP>(pool[ri * ld_pool + v_off + g * E + e]);
-            x[i][c] = val;
-          }
-        }
+            if (e < E) {
+              const float x = is_pool ? pooled[ri * ld_pooled + v_off + g * E + e]
+                                      : to_float<TP>(pool[ri * ld_pool + v_off + g * E + e]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-#pragma unroll
-          for (int r = 0; r < RH; ++r) {
-            const float pw = __shfl_sync(0xffffffffu, pj[r], (j0 + i) & 31);
-            if (j0 + i < cnt) {
-#pragma unroll
-              for (int c = 0; c < kPwMaxCols; ++c) acc[r][c] = fmaf(pw, x[i][c], acc[r][c]);
+              for (int r = 0; r < RH; ++r) acc[r][c] = fmaf(pw[r], x, acc[r][c]);
             }
           }
         }
@@ -338,7 +392,7 @@ pooled_window_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __
       }
 #pragma unroll
       for (int c = 0; c < kPwMaxCols; ++c) {
-        const int e = lane + 32 * c;
+        const int e = vblk ? 128 * (c / 4) + 4 * lane + (c & 3) : lane + 32 * c;
         if (e < E) wacc[(warp * RH + r) * E + e] = acc[r][c];
       }
     }
@@ -514,7 +568,10 @@ static int pooled_window_attn_impl(const float* q, int64_t ldq, const void* pool
                    (!vfreq_hi || E % 2 == 0),
                "b200_pooled_window_attn: heads %d / %d, key size %d, value size %d (max %d), block %d", H,
                G, D, E, 32 * kPwMaxCols, P);
-  int nw = max_keys <= 0 ? 4 : min(kPwMaxWarps, max(4, ceil_div(max_keys, 64)));
+  // one warp per 64 keys of the longest list (a hint; 0 = unknown), at least 4; the block part has few
+  // keys per row and many rows: one warp per 32 blocks
+  int nw = part_out ? min(kPwMaxWarps, max(1, ceil_div(max(max_keys, 1), 32)))
+                    : (max_keys <= 0 ? 4 : min(kPwMaxWarps, max(4, ceil_div(max_keys, 64))));
   auto smem_for = [&](int w) {
     return sizeof(float) * (static_cast<size_t>(kPwHeads) * D + static_cast<size_t>(w) * kPwHeads * (E + 3) +
                             kPwHeads + static_cast<size_t>(kPwHeads) * E + E + 4);

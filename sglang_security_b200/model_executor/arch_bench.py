@@ -470,7 +470,7 @@ def bench_kisilix(name, s, steps, warmup, device="cuda"):
             runner.release(r)
 
     names = ["delta_recurrence", "ssm_recurrence", "causal_conv_silu", "gated_group_rmsnorm", "pooled_window_attn",
-             "attn_extend", "headnorm_rot_write", "pool_block_means", "moe_grouped_gemm", "moe_route", "moe_align",
+             "attn_extend", "pooled_merge_unrotate", "headnorm_rot_write", "pool_block_means", "moe_grouped_gemm", "moe_route", "moe_align",
              "scaled_add_layernorm", "act_and_mul"]
     row = {"arch": "kisilix", "size": name}
     ms = _timed(prefill, steps, warmup)
