@@ -177,7 +177,7 @@ moe_route_grouped_kernel(const T* __restrict__ h, int64_t ldh, const float* __re
       g_s[g] = gm;
     }
     __syncwarp();
-    // the `keep` best groups, one per round (ties: lowest index); a kept group's score becomes +inf
+    // the `keep` best groups, one per pass (ties: lowest index); a kept group's score becomes +inf
     for (int k = 0; k < keep; ++k) {
       float bv = -INFINITY;
       int bi = 0x7fffffff;
